@@ -19,7 +19,7 @@ from .manager import CacheGroup, flat_requests
 def bytes_per_page(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype) -> int:
     """Bytes one page id costs when every group gets the same number of pages."""
     el = torch.empty((), dtype=dtype).element_size()
-    return sum(len(g.cache_ids) * g.num_kv_heads * page_size * (g.head_dim + (0 if g.shared else (g.v_head_dim or g.head_dim))) * el
+    return sum(len(g.cache_ids) * g.num_kv_heads * page_size * (g.head_dim + (0 if g.shared else (g.v_head_dim or g.head_dim))) * el // max(1, g.every)
                for g in groups)
 
 

@@ -32,6 +32,7 @@ class CacheGroup:
                                      # member of a cache id that asked for a tuple
     shared: bool = False             # one vector a token is key and value at once
     v_head_dim: int = 0              # size of a value head when it differs from the keys' (0: the same)
+    every: int = 1                   # P > 1: the group holds one entry for every P tokens of a sequence (n // P for n tokens)
 
 
 def flat_requests(requests: Sequence[KVPages | StateSlot | None | tuple]) -> list[tuple[object, object]]:
@@ -52,10 +53,11 @@ def plan_groups(requests: Sequence[KVPages | StateSlot | None | tuple]) -> tuple
     state_ids: list = []
     for key, r in flat_requests(requests):
         if isinstance(r, KVPages):
-            by_key.setdefault((r.num_kv_heads, r.head_dim, r.window, r.shared, r.v_head_dim if r.v_head_dim != r.head_dim else 0), []).append(key)
+            by_key.setdefault((r.num_kv_heads, r.head_dim, r.window, r.shared, r.v_head_dim if r.v_head_dim != r.head_dim else 0,
+                               max(1, r.every)), []).append(key)
         elif isinstance(r, StateSlot):
             state_ids.append(key)
-    groups = [CacheGroup(k[0], k[1], k[2], tuple(v), k[3], k[4]) for k, v in by_key.items()]
+    groups = [CacheGroup(k[0], k[1], k[2], tuple(v), k[3], k[4], k[5]) for k, v in by_key.items()]
     return groups, state_ids
 
 
@@ -111,11 +113,17 @@ class CacheManager:
         w = self.groups[g].window
         return max(0, start - w + 1) // self.page_size if w > 0 else 0
 
+    def pages_for(self, g: int, length: int) -> int:
+        """Pages of group g that back a sequence of `length` tokens: one entry a token, or one for every whole block of
+        `every` tokens."""
+        every = self.groups[g].every
+        entries = length // every if every > 1 else length
+        return -(-entries // self.page_size)
+
     def pages_needed(self, rid: Hashable, new_length: int) -> list[int]:
         """Pages each group has to take so that positions below new_length are backed."""
         rc = self._requests[rid]
-        want = -(-new_length // self.page_size)
-        return [max(0, want - len(t)) for t in rc.tables]
+        return [max(0, self.pages_for(g, new_length) - len(t)) for g, t in enumerate(rc.tables)]
 
     def can_extend(self, rid: Hashable, new_length: int) -> bool:
         return all(self.pools[g].can_allocate(n) for g, n in enumerate(self.pages_needed(rid, new_length)))
@@ -144,17 +152,17 @@ class CacheManager:
         reqs = [self._requests[rid] for rid in rids]
         need = [0] * len(self.groups)
         for rc in reqs:
-            want = rc.length // ps + 1                       # pages that back positions 0 .. length
             for g, t in enumerate(rc.tables):
+                want = self.pages_for(g, rc.length + 1)      # pages that back positions 0 .. length
                 if want > len(t):
                     need[g] += want - len(t)
         if any(need) and not all(self.pools[g].can_allocate(n) for g, n in enumerate(need)):
             return None
         starts = []
         for rc in reqs:
-            want = rc.length // ps + 1
             grew = False
             for g, t in enumerate(rc.tables):
+                want = self.pages_for(g, rc.length + 1)
                 while len(t) < want:
                     t.append(self.pools[g].allocate())
                     grew = True
@@ -178,7 +186,8 @@ class CacheManager:
         rc = self._requests[rid]
         best = upto
         for g, t in enumerate(rc.tables):
-            best = min(best, (len(t) + self.pools[g].num_free) * self.page_size)
+            every = self.groups[g].every
+            best = min(best, (len(t) + self.pools[g].num_free) * self.page_size * every + (every - 1))
         return max(min(best, upto), rc.length)
 
     def release_behind_window(self, rid: Hashable) -> int:

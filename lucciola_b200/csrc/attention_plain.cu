@@ -15,6 +15,12 @@
 // Two more things lucciola does not have.  Values may have another size than keys (v_dim; the value pool is
 // then [page][kv_head][slot][v_dim]).  And a linear distance bias: with `slopes` (one 32-bit number a query
 // head) the score of key j for the query at position i is (q . k) * scale - slopes[h] * (i - j).
+//
+// Three more options.  A capped score: s <- softcap * tanh(s / softcap).  A sink: with `sinks` (one 32-bit number a
+// query head) the softmax's denominator also holds exp(sinks[h]), which has no key and no value.  And pooled
+// blocks behind the window: with pool = P > 0 the query at position i also sees entry b of a second paged cache (one
+// entry for every P tokens, at "position" b of its own block table) for every b with (b + 1) P - 1 <= i - window,
+// in the same softmax; the entries are the means that lb_pool_kv writes.
 #include "common.cuh"
 
 namespace lb {
@@ -26,6 +32,10 @@ struct PlainAttnParams {
   float scale;
   int v_dim;               // size of a value head
   const float* slopes;     // optional [num_q_heads]: distance bias
+  float softcap;           // 0: scores are not capped
+  const float* sinks;      // optional [num_q_heads]
+  int pool;                // 0: no pooled blocks; P: one pooled entry for every P tokens
+  const void* pool_k; const void* pool_v; const int* pool_table; int pool_max_pages;
 };
 
 template <typename T, int DPL>
@@ -56,39 +66,60 @@ __global__ void plain_attention_kernel(PlainAttnParams p) {
 #pragma unroll
   for (int i = 0; i < DPL; ++i) o[i] = 0.f;
 
-  for (int base = lo; base <= pos; base += 32) {
-    const int j = base + lane;
-    const bool valid = j <= pos;
-    long long off = -1;                        // the key's place in its pool, in heads
-    float s = -INFINITY;
-    if (valid) {
-      const int page = bt[j / p.page_size];
-      if (page >= 0) {
-        off = ((long long)page * p.num_kv_heads + kvh) * p.page_size + (j % p.page_size);
-        const T* k = kc + off * d;
-        float acc = 0.f;
-        for (int i = 0; i < d; ++i) acc += qs[i] * to_f32(k[i]);
-        s = acc * p.scale - slope * (float)(pos - j);
+  // keys j0 .. j1 - 1 of one paged cache, 32 at a time (a lane a key), through the online softmax
+  auto visit = [&](const T* kc, const T* vc, const int* bt, int j0, int j1, bool biased) {
+    for (int base = j0; base < j1; base += 32) {
+      const int j = base + lane;
+      const bool valid = j < j1;
+      long long off = -1;                        // the key's place in its pool, in heads
+      float s = -INFINITY;
+      if (valid) {
+        const int page = bt[j / p.page_size];
+        if (page >= 0) {
+          off = ((long long)page * p.num_kv_heads + kvh) * p.page_size + (j % p.page_size);
+          const T* k = kc + off * d;
+          float acc = 0.f;
+          for (int i = 0; i < d; ++i) acc += qs[i] * to_f32(k[i]);
+          s = acc * p.scale;
+          if (biased) s -= slope * (float)(pos - j);
+          if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+        }
       }
+      const float m_new = fmaxf(m, warp_max(s));
+      if (m_new == -INFINITY) continue;          // no key of this round has a page: uniform over the warp
+      const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
+      const float pj = (off >= 0) ? expf(s - m_new) : 0.f;
+      l = l * alpha + warp_sum(pj);
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) o[i] *= alpha;
+      const int n = min(32, j1 - base);
+      for (int jj = 0; jj < n; ++jj) {
+        const float pv = __shfl_sync(0xffffffffu, pj, jj);
+        const long long voff = __shfl_sync(0xffffffffu, off, jj);
+        if (voff < 0) continue;  // uniform over the warp
+        const T* v = vc + voff * dv;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+          const int dim = lane + 32 * i;
+          if (dim < dv) o[i] += pv * to_f32(v[dim]);
+        }
+      }
+      m = m_new;
     }
-    const float m_new = fmaxf(m, warp_max(s));
+  };
+  visit(kc, vc, bt, lo, pos + 1, true);
+  if (p.pool > 0 && p.window > 0) {
+    const int nb = (pos - p.window + 1) / p.pool;          // blocks that end at or before pos - window (negative: none)
+    if (nb > 0)
+      visit((const T*)p.pool_k, (const T*)p.pool_v, p.pool_table + (size_t)p.token_seq[t] * p.pool_max_pages, 0, nb, false);
+  }
+  if (p.sinks) {
+    const float sink = p.sinks[h];
+    const float m_new = fmaxf(m, sink);
     const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    const float pj = (off >= 0) ? expf(s - m_new) : 0.f;
-    l = l * alpha + warp_sum(pj);
+    l = l * alpha + expf(sink - m_new);
 #pragma unroll
     for (int i = 0; i < DPL; ++i) o[i] *= alpha;
-    const int n = min(32, pos - base + 1);
-    for (int jj = 0; jj < n; ++jj) {
-      const float pv = __shfl_sync(0xffffffffu, pj, jj);
-      const long long voff = __shfl_sync(0xffffffffu, off, jj);
-      if (voff < 0) continue;  // uniform over the warp
-      const T* v = vc + voff * dv;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) {
-        const int dim = lane + 32 * i;
-        if (dim < dv) o[i] += pv * to_f32(v[dim]);
-      }
-    }
     m = m_new;
   }
   T* out = (T*)p.out + ((size_t)t * p.num_q_heads + h) * dv;
@@ -120,7 +151,12 @@ LB_EXPORT int lb_attention_plain(int dtype, const void* q, void* out, const void
                                  const void* v_cache, const int* positions, const int* token_seq,
                                  const int* block_table, int num_tokens, int num_q_heads,
                                  int num_kv_heads, int head_dim, int page_size, int max_pages,
-                                 int window, float scale, int v_dim, const float* slopes, cudaStream_t stream) {
+                                 int window, float scale, int v_dim, const float* slopes, float softcap,
+                                 const float* sinks, int pool, const void* pool_k, const void* pool_v, const int* pool_table,
+                                 int pool_max_pages, cudaStream_t stream) {
+  LB_CHECK_ARG(pool == 0 || (pool > 0 && window > 0 && pool_k && pool_v && pool_table && pool_max_pages > 0),
+               "attention_plain: pooled blocks need a window, the pooled cache and its block table");
+  LB_CHECK_ARG(softcap >= 0.f, "attention_plain: a cap of %f", (double)softcap);
   if (v_dim <= 0) v_dim = head_dim;
   LB_CHECK_ARG(v_dim <= 512, "attention_plain: value size %d not in 1..512", v_dim);
   LB_CHECK_ARG(lb::valid_dtype(dtype), "attention_plain: bad dtype %d", dtype);
@@ -136,6 +172,8 @@ LB_EXPORT int lb_attention_plain(int dtype, const void* q, void* out, const void
   p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
   p.page_size = page_size; p.max_pages = max_pages; p.window = window; p.scale = scale; p.v_dim = v_dim; p.slopes = slopes;
+  p.softcap = softcap; p.sinks = sinks; p.pool = pool; p.pool_k = pool_k; p.pool_v = pool_v; p.pool_table = pool_table;
+  p.pool_max_pages = pool_max_pages;
   LB_DISPATCH_DTYPE(dtype, T, { lb::launch_plain<T>(p, num_tokens, stream); })
   LB_CHECK_LAUNCH("attention_plain");
   return 0;

@@ -350,3 +350,87 @@ LB_EXPORT int lb_add_rmsnorm(void* out, int out_dtype, float* residual, const vo
   LB_CHECK_LAUNCH("add_rmsnorm");
   return 0;
 }
+
+// Two norms of one stream, and the sum of two normed rows: what a block needs whose two sublayers read the same
+// residual stream through a norm each, and a mixer that adds two outputs after norming each over the model width.
+//
+// lb_add_rmsnorm_pair: residual += delta_a + delta_b (each optional, 32-bit sum, in place); then, with
+// f = 1 / sqrt(mean(residual^2) + eps), out_a = residual * f * w_a and (optional) out_b = residual * f * w_b: the
+// two norms share the row's root mean square and differ in their weights only.
+// lb_rmsnorm_mix2: out = sa * a / rms(a) * w_a + sb * b / rms(b) * w_b, 32-bit rows in and out.
+// One CTA a row, sums in an order that the row's size fixes.
+namespace lb {
+
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_pair_kernel(TO* __restrict__ out_a, TO* __restrict__ out_b, float* __restrict__ residual,
+                                        const TD* __restrict__ delta_a, const TD* __restrict__ delta_b,
+                                        const float* __restrict__ w_a, const float* __restrict__ w_b, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = residual[base + i];
+    if (delta_a) v += to_f32(delta_a[base + i]);
+    if (delta_b) v += to_f32(delta_b[base + i]);
+    if (delta_a || delta_b) residual[base + i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = residual[base + i] * inv;
+    out_a[base + i] = from_f32<TO>(v * w_a[i]);
+    if (out_b) out_b[base + i] = from_f32<TO>(v * w_b[i]);
+  }
+}
+
+__global__ void rmsnorm_mix2_kernel(float* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                    const float* __restrict__ w_a, const float* __restrict__ w_b, float sa, float sb, int hidden,
+                                    float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float ssa = 0.f, ssb = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float x = a[base + i], y = b[base + i];
+    ssa += x * x;
+    ssb += y * y;
+  }
+  ssa = block_sum(ssa, scratch);
+  ssb = block_sum(ssb, scratch);
+  const float fa = sa / sqrtf(ssa / (float)hidden + eps), fb = sb / sqrtf(ssb / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    out[base + i] = a[base + i] * fa * w_a[i] + b[base + i] * fb * w_b[i];
+}
+
+}  // namespace lb
+
+LB_EXPORT int lb_add_rmsnorm_pair(void* out_a, void* out_b, int out_dtype, float* residual, const void* delta_a,
+                                  const void* delta_b, int delta_dtype, const float* w_a, const float* w_b, int num_rows,
+                                  int hidden, float eps, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(out_dtype) && lb::valid_dtype(delta_dtype), "add_rmsnorm_pair: bad dtype");
+  LB_CHECK_ARG(out_a && residual && w_a && (!out_b || w_b) && num_rows >= 0 && hidden > 0, "add_rmsnorm_pair: bad arguments");
+  if (num_rows == 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  LB_DISPATCH_DTYPE(delta_dtype, TD, {
+    LB_DISPATCH_DTYPE(out_dtype, TO, {
+      lb::launch(lb::add_rmsnorm_pair_kernel<TD, TO>, dim3(num_rows), dim3(threads), 0, stream, (TO*)out_a, (TO*)out_b, residual,
+                 (const TD*)delta_a, (const TD*)delta_b, w_a, w_b, hidden, eps);
+    })
+  })
+  LB_CHECK_LAUNCH("add_rmsnorm_pair");
+  return 0;
+}
+
+LB_EXPORT int lb_rmsnorm_mix2(float* out, const float* a, const float* b, const float* w_a, const float* w_b, float sa, float sb,
+                              int num_rows, int hidden, float eps, cudaStream_t stream) {
+  LB_CHECK_ARG(out && a && b && w_a && w_b && num_rows >= 0 && hidden > 0, "rmsnorm_mix2: bad arguments");
+  if (num_rows == 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  lb::launch(lb::rmsnorm_mix2_kernel, dim3(num_rows), dim3(threads), 0, stream, out, a, b, w_a, w_b, sa, sb, hidden, eps);
+  LB_CHECK_LAUNCH("rmsnorm_mix2");
+  return 0;
+}

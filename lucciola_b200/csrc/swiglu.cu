@@ -89,3 +89,43 @@ LB_EXPORT int lb_swiglu(int dtype, void* out, const void* gate, const void* up, 
   LB_CHECK_LAUNCH("swiglu");
   return 0;
 }
+
+// Activations of a feed-forward without a gate, out = act(x), computed in 32-bit and rounded once.  `act`:
+// 0 silu, 1 relu, 2 the tanh form of gelu, 4 xIELU with its two positive numbers a_p, a_n (p0, p1):
+//   x > 0: a_p x^2 + x / 2        x <= 0: a_n (exp(x) - 1 - x) + x / 2
+// (the design's learned numbers p, q enter as a_p = softplus(p), a_n = 1/2 + softplus(q), formed once on the host).
+namespace lb {
+
+__device__ __forceinline__ float plain_act(int act, float p0, float p1, float x) {
+  if (act == 4) return x > 0.f ? fmaf(p0 * x, x, 0.5f * x) : fmaf(p1, expm1f(x) - x, 0.5f * x);
+  return gated_act(act, 0.f, x, 1.f);
+}
+
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ out, const T* __restrict__ x, long long in_stride, int n, long long total,
+                                  int act, float p0, float p1) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / n;
+    const int c = (int)(idx - t * n);
+    out[idx] = from_f32<T>(plain_act(act, p0, p1, to_f32(x[t * in_stride + c])));
+  }
+}
+
+}  // namespace lb
+
+LB_EXPORT int lb_activation(int dtype, void* out, const void* x, long long in_stride, int num_tokens, int n, int act, float p0,
+                            float p1, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(dtype), "activation: bad dtype %d", dtype);
+  LB_CHECK_ARG(out && x && num_tokens >= 0 && n > 0 && in_stride >= n, "activation: bad sizes");
+  LB_CHECK_ARG(act == 0 || act == 1 || act == 2 || act == 4, "activation: %d is none of silu (0), relu (1), gelu_tanh (2), xielu (4)", act);
+  if (num_tokens == 0) return 0;
+  const long long total = (long long)num_tokens * n;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  LB_DISPATCH_DTYPE(dtype, T, {
+    lb::launch(lb::activation_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out, (const T*)x, in_stride, n, total, act, p0, p1);
+  })
+  LB_CHECK_LAUNCH("activation");
+  return 0;
+}

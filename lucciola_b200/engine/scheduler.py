@@ -69,8 +69,8 @@ class Scheduler:
         if n >= self.max_model_len:
             raise ValueError(f"the prompt has {n} tokens; with max_model_len {self.max_model_len} nothing could be generated")
         most = min(n + req.params.max_new_tokens, self.max_model_len)
-        pages = -(-most // self.manager.page_size)
         for g, pool in enumerate(self.manager.pools):
+            pages = self.manager.pages_for(g, most)
             if pages > pool.num_pages:
                 raise ValueError(
                     f"the request may grow to {most} tokens = {pages} pages, the pool of cache group {g} has {pool.num_pages}")
@@ -96,7 +96,7 @@ class Scheduler:
     def _pages_needed(self, r: Request, new_len: int) -> list[int]:
         if self.manager.has_request(r.rid):
             return self.manager.pages_needed(r.rid, new_len)
-        return [-(-new_len // self.manager.page_size)] * len(self.manager.pools)
+        return [self.manager.pages_for(g, new_len) for g in range(len(self.manager.pools))]
 
     def _fits(self, need: Sequence[int], reserved: Sequence[int]) -> bool:
         return all(p.num_free - reserved[g] >= need[g] for g, p in enumerate(self.manager.pools))
@@ -107,7 +107,8 @@ class Scheduler:
         best = upto
         for g, p in enumerate(self.manager.pools):
             have = len(self.manager.block_table(r.rid, g)) if self.manager.has_request(r.rid) else 0
-            best = min(best, (have + p.num_free - reserved[g]) * ps)
+            every = self.manager.groups[g].every       # a group with one entry for every `every` tokens
+            best = min(best, (have + p.num_free - reserved[g]) * ps * every + (every - 1))
         return best
 
     def _release(self, rid: Hashable) -> None:

@@ -132,9 +132,10 @@ class ModelRunner:
         self.max_model_len = options.max_model_len or positions
         if self.max_model_len > positions:
             raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's {positions} positions")
-        self.manager = CacheManager(self.groups, self.page_size, self.num_pages, options.max_num_seqs)
-        self.cache = DeviceCache(requests, self.groups, self.page_size, [self.num_pages] * len(self.groups),
-                                 options.max_num_seqs, rt.act_dtype, self.device)
+        # a group with one entry for every P tokens needs a P-th of the pages, and one more for each sequence's last, partly filled one
+        counts = [self.num_pages if g.every <= 1 else -(-self.num_pages // g.every) + options.max_num_seqs for g in self.groups]
+        self.manager = CacheManager(self.groups, self.page_size, counts, options.max_num_seqs)
+        self.cache = DeviceCache(requests, self.groups, self.page_size, counts, options.max_num_seqs, rt.act_dtype, self.device)
         self.max_pages_per_seq = -(-self.max_model_len // self.page_size)
         self._any_window = any(g.window > 0 for g in self.groups)
         self._arange_cache = np.arange(512, dtype=np.int32)
@@ -171,7 +172,7 @@ class ModelRunner:
                 n = self.manager.pages_needed(e.rid, self.manager.length(e.rid) + len(e.tokens))
             else:
                 new_requests += 1
-                n = [-(-len(e.tokens) // self.page_size)] * len(self.groups)
+                n = [self.manager.pages_for(g, len(e.tokens)) for g in range(len(self.groups))]
             need = [a + b for a, b in zip(need, n)]
         if new_requests > len(self.manager._free_slots):
             return False

@@ -68,7 +68,23 @@ _SIGNATURES = {
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "lb_attention_plain": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_float, c_void_p, c_int,
+                           c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "lb_short_conv": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_int, c_int, c_int, c_int, c_void_p],
+    "lb_short_conv_state": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lb_state_recurrence": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                            c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "lb_gated_group_norm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "lb_bias_rmsnorm_cols": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
+    "lb_pool_kv": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_add_rmsnorm_pair": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                            c_float, c_void_p],
+    "lb_rmsnorm_mix2": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_float, c_void_p],
+    "lb_activation": [c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "lb_swiglu": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_void_p],
     "lb_gemm_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                       c_longlong, c_void_p],
@@ -305,10 +321,19 @@ def rope_kv(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, q_out: t
 def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                    stream: int, v_dim: int = 0, slopes: torch.Tensor | None = None) -> None:
+                    stream: int, v_dim: int = 0, slopes: torch.Tensor | None = None, softcap: float = 0.0,
+                    sinks: torch.Tensor | None = None, pool: int = 0, pool_k: torch.Tensor | None = None,
+                    pool_v: torch.Tensor | None = None, pool_table: torch.Tensor | None = None) -> None:
     """`v_dim`: the size of a value head if it is not head_dim (out is then [T, heads, v_dim]); `slopes` (float32
-    [heads]): the score of key j for the query at position i is lowered by slopes[h] * (i - j)."""
+    [heads]): the score of key j for the query at position i is lowered by slopes[h] * (i - j).  `softcap` > 0: scores
+    become softcap * tanh(score / softcap).  `sinks` (float32 [heads]): exp(sinks[h]) joins the softmax's denominator.
+    `pool` = P > 0 with a window: the query at i also sees entry b of the pooled cache (pool_k, pool_v through
+    pool_table, one entry for every P tokens) for every b with (b + 1) P - 1 <= i - window."""
     dt = q.dtype
+    if sinks is not None:
+        _check(sinks, "sinks", torch.float32)
+    if pool:
+        _check(pool_k, "pooled k", dt); _check(pool_v, "pooled v", dt); _check(pool_table, "pooled block table", torch.int32)
     if slopes is not None:
         _check(slopes, "distance slopes", torch.float32)
     _check(q, "q"); _check(out, "attention output", dt); _check(k_cache, "k pool", dt); _check(v_cache, "v pool", dt)
@@ -316,7 +341,148 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     _check(block_table, "block table", torch.int32)
     _call("lb_attention_plain", dtype_code(dt), q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), q.shape[0], num_q_heads, num_kv_heads,
-          head_dim, page_size, block_table.shape[1], window, scale, v_dim, _ptr(slopes), stream)
+          head_dim, page_size, block_table.shape[1], window, scale, v_dim, _ptr(slopes), softcap, _ptr(sinks), pool,
+          _ptr(pool_k) if pool else None, _ptr(pool_v) if pool else None, _ptr(pool_table) if pool else None,
+          pool_table.shape[1] if pool else 0, stream)
+
+
+def _rows32(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what} must be float32 rows on the GPU with unit column stride")
+
+
+def short_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor | None,
+               step, stream: int, act: bool = True) -> None:
+    """out_t = act(bias + sum_j weight[j, :] * x_(t - taps + 1 + j)) over each sequence's tokens in order (weight
+    [taps, channels] float32, oldest tap first; act: silu); x and out are float32 rows [T, channels] that may be column
+    ranges of wider matrices; what lies before a portion is read from state[slot] ([taps - 1, channels] float32).  The
+    state is not changed."""
+    _rows32(out, "convolution output"); _rows32(x, "convolution input"); _check(weight, "taps", torch.float32)
+    T, C = x.shape
+    taps = weight.shape[0]
+    if weight.shape[1] != C or tuple(out.shape) != (T, C):
+        raise KernelError(f"the taps are {tuple(weight.shape)} for rows of {C}, the output {tuple(out.shape)}")
+    if bias is not None:
+        _check(bias, "convolution bias", torch.float32)
+    if state is not None:
+        _check(state, "convolution state", torch.float32)
+    _call("lb_short_conv", out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), _ptr(state),
+          step.token_seq.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), T, C, taps, 1 if act else 0, stream)
+
+
+def short_conv_state(state: torch.Tensor, x: torch.Tensor, taps: int, step, stream: int) -> None:
+    """state[slot] = the last taps - 1 rows of (state[slot] ++ this step's rows of the sequence); float32."""
+    _check(state, "convolution state", torch.float32); _rows32(x, "convolution input")
+    _call("lb_short_conv_state", state.data_ptr(), x.data_ptr(), x.stride(0), step.cu_tokens.data_ptr(),
+          step.state_slots.data_ptr(), step.num_seqs, x.shape[1], taps, stream)
+
+
+def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None,
+                     A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
+                     step, heads: int, groups: int, dim: int, vdim: int, stream: int, delta: bool, unit_norm: bool = False,
+                     q_scale: float = 1.0, unit_eps: float = 1e-6) -> None:
+    """A recurrence with a decay and a write strength per token over this step's tokens (csrc/state_recurrence.cu):
+    delta=True the gated delta rule (b: beta's input), else the state space of Mamba-2 (k = B, q = C, v = x, a = dt's
+    input, D optional).  q, k [T, groups * dim], v [T, heads * vdim], a, b [T, heads]: float32 rows, column ranges allowed;
+    state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32."""
+    for t, w in ((q, "q"), (k, "k"), (v, "v"), (a, "a")) + (((b, "b"),) if b is not None else ()):
+        _rows32(t, w)
+    _rows32(out, "recurrence output")
+    _check(A_log, "A_log", torch.float32); _check(dt_bias, "dt_bias", torch.float32); _check(state, "recurrent state", torch.float32)
+    if D is not None:
+        _check(D, "D", torch.float32)
+    T = q.shape[0]
+    if (tuple(q.shape) != (T, groups * dim) or tuple(k.shape) != (T, groups * dim) or tuple(v.shape) != (T, heads * vdim)
+            or tuple(a.shape) != (T, heads) or tuple(out.shape) != (T, heads * vdim) or tuple(state.shape[1:]) != (heads, dim, vdim)):
+        raise KernelError("the recurrence's operands do not fit its head counts and sizes")
+    _call("lb_state_recurrence", 1 if delta else 0, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+          a.data_ptr(), a.stride(0), _ptr(b), b.stride(0) if b is not None else 0, A_log.data_ptr(), dt_bias.data_ptr(), _ptr(D),
+          state.data_ptr(), out.data_ptr(), out.stride(0), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs,
+          heads, groups, dim, vdim, 1 if unit_norm else 0, q_scale, unit_eps, stream)
+
+
+def gated_group_norm(out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
+                     stream: int, gate_first: bool = False, act: str = "silu", scale: float = 1.0) -> None:
+    """The norm behind a recurrence, in `groups` equal parts of a row, with a gate: out = y / rms_part(y) * w * act(gate),
+    or with gate_first z = y * act(gate), out = z / rms_part(z) * w.  y, gate: float32 rows (column ranges allowed); weight
+    float32 of the row's size, or of a part's size (then shared by the parts); out rows of any type."""
+    _rows32(y, "norm input"); _rows32(gate, "gate"); _check(weight, "norm weight", torch.float32)
+    T, n = y.shape
+    if out.stride(1) != 1 or tuple(out.shape) != (T, n) or tuple(gate.shape) != (T, n) or n % groups or weight.numel() not in (n, n // groups):
+        raise KernelError("the gated norm's operands do not fit")
+    _call("lb_gated_group_norm", out.data_ptr(), dtype_code(out.dtype), out.stride(0), y.data_ptr(), y.stride(0), gate.data_ptr(),
+          gate.stride(0), weight.data_ptr(), weight.numel(), T, n, groups, 1 if gate_first else 0, {"silu": 0, "sigmoid": 1}[act],
+          eps, scale, stream)
+
+
+def bias_rmsnorm_cols(x: torch.Tensor, ranges, eps: float, stream: int) -> None:
+    """In place on float32 rows: for each of up to three (first column, size, bias or None, norm weight or None):
+    x[:, range] += bias, then, with a weight, the RMS norm over the whole range times the weight."""
+    _rows32(x, "rows")
+    n = len(ranges)
+    if not 1 <= n <= 3:
+        raise KernelError("one to three column ranges")
+    for _, _, b, w in ranges:
+        for t in (b, w):
+            if t is not None:
+                _check(t, "bias or weight", torch.float32)
+    cols = (c_int * 3)(*[r[0] for r in ranges])
+    sizes = (c_int * 3)(*[r[1] for r in ranges])
+    biases = (c_void_p * 3)(*[_ptr(r[2]) for r in ranges])
+    weights = (c_void_p * 3)(*[_ptr(r[3]) for r in ranges])
+    _call("lb_bias_rmsnorm_cols", x.data_ptr(), x.stride(0), x.shape[0], n, cols, sizes, biases, weights, eps, stream)
+
+
+def pool_kv(k_cache: torch.Tensor, v_cache: torch.Tensor, table: torch.Tensor, pool_k: torch.Tensor, pool_v: torch.Tensor,
+            pool_table: torch.Tensor, step, num_kv_heads: int, head_dim: int, v_dim: int, page_size: int, pool: int,
+            stream: int) -> None:
+    """The mean key and value of every block of `pool` tokens that this step completes, from the pages into the pooled
+    cache (entry b of a sequence at place b of its pooled block table)."""
+    dt = k_cache.dtype
+    _check(k_cache, "k pool", dt); _check(v_cache, "v pool", dt); _check(pool_k, "pooled k", dt); _check(pool_v, "pooled v", dt)
+    _check(table, "block table", torch.int32); _check(pool_table, "pooled block table", torch.int32)
+    _call("lb_pool_kv", dtype_code(dt), k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.shape[1], pool_k.data_ptr(),
+          pool_v.data_ptr(), pool_table.data_ptr(), pool_table.shape[1], step.cu_tokens.data_ptr(), step.context_lens.data_ptr(),
+          step.num_seqs, step.max_q_len // pool + 1, num_kv_heads, head_dim, v_dim, page_size, pool, stream)
+
+
+def add_rmsnorm_pair(out_a: torch.Tensor, out_b: torch.Tensor | None, residual: torch.Tensor, deltas: tuple, w_a: torch.Tensor,
+                     w_b: torch.Tensor | None, eps: float, stream: int) -> None:
+    """residual += the deltas (none, one or two, of one type); out_a = rmsnorm(residual) * w_a and, if given,
+    out_b = rmsnorm(residual) * w_b: two norms of one stream that differ in their weights."""
+    _check(out_a, "norm output"); _check(residual, "residual", torch.float32); _check(w_a, "norm weight", torch.float32)
+    ds = [d for d in deltas if d is not None]
+    if len(ds) > 2 or any(d.dtype != ds[0].dtype for d in ds):
+        raise KernelError("at most two deltas, of one type")
+    for d in ds:
+        _check(d, "delta")
+    if out_b is not None:
+        _check(out_b, "second norm output", out_a.dtype); _check(w_b, "second norm weight", torch.float32)
+    _call("lb_add_rmsnorm_pair", out_a.data_ptr(), _ptr(out_b), dtype_code(out_a.dtype), residual.data_ptr(),
+          ds[0].data_ptr() if ds else None, ds[1].data_ptr() if len(ds) > 1 else None, dtype_code(ds[0].dtype) if ds else F32,
+          w_a.data_ptr(), _ptr(w_b), out_a.shape[0], out_a.shape[1], eps, stream)
+
+
+def rmsnorm_mix2(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, w_a: torch.Tensor, w_b: torch.Tensor, sa: float, sb: float,
+                 eps: float, stream: int) -> None:
+    """out = sa * rmsnorm(a) * w_a + sb * rmsnorm(b) * w_b, float32 rows."""
+    for t in (out, a, b, w_a, w_b):
+        _check(t, "operand of the normed sum", torch.float32)
+    _call("lb_rmsnorm_mix2", out.data_ptr(), a.data_ptr(), b.data_ptr(), w_a.data_ptr(), w_b.data_ptr(), sa, sb, a.shape[0],
+          a.shape[1], eps, stream)
+
+
+# Activations of a feed-forward without a gate (csrc/swiglu.cu, lb_activation).
+PLAIN_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "xielu": 4}
+
+
+def activation(out: torch.Tensor, x: torch.Tensor, act: str, stream: int, p0: float = 0.0, p1: float = 0.0) -> None:
+    """out = act(x) (see PLAIN_ACTS; xielu takes its two positive numbers a_p, a_n as p0, p1); x rows may be a column range."""
+    _check(out, "activation output", x.dtype)
+    if x.stride(1) != 1 or out.shape != x.shape:
+        raise KernelError("the activation's input needs unit column stride and the output's shape")
+    _call("lb_activation", dtype_code(out.dtype), out.data_ptr(), x.data_ptr(), x.stride(0), x.shape[0], x.shape[1], PLAIN_ACTS[act],
+          p0, p1, stream)
 
 
 # Activations of a gated feed-forward, out = act(gate) * up: silu, relu, the tanh form of gelu, and "clamped_swish",

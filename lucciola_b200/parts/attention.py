@@ -281,3 +281,97 @@ class GatedBiasAttention(GQAttention):
         inner = self.rt.empty((h.shape[0], self.inner_size))
         self.inner(pre, step, cache, inner, 1.0, write_cache)
         return self.o.forward(inner)
+
+
+class PooledWindowAttention(Mixer):
+    """Softmax attention over a sliding window and, behind it, over one mean key and value for every whole block of
+    `pool` tokens, with biases, a norm over the whole q and k projections, partial rotation, a capped score and a sink:
+
+        q = rmsnorm_all(W_q x + b_q) * n_q     k = rmsnorm_all(W_k x + b_k) * n_k     v = W_v x + b_v
+            (the root mean square runs over ALL heads of the projection at once; then the first rot_dims entries of
+             each head of q and k are rotated, half-rotation pairing)
+        the query at position i sees the keys j with 0 <= i - j < window, and block b (tokens b P .. b P + P - 1) through the
+            mean of its P keys and the mean of its P values, as the cache holds them, if b P + P - 1 <= i - window
+        s = softcap * tanh((q . k) * scale / softcap)
+        out_h = sum_j exp(s_j) v_j / (sum_j exp(s_j) + exp(sink_h))          tokens and blocks in one softmax
+
+    The keys and values of the last max(window, P) tokens stay in pages (a window group, whose pages go back as the
+    window passes); the blocks' means live in a second group of pages with one entry for every P tokens
+    (KVPages(every=P)), written by the step that completes a block.  W_q | W_k | W_v are one product with 32-bit output.
+
+    Beside forward(), the mixer offers its steps apart (in_names / in_sizes, inner, `o`)."""
+    recordable = True
+
+    def __init__(self, rt: Runtime, prefix: str, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                 softcap: float, position_encoding: Optional[PositionEncoding], window: int, pool: int, eps: float):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
+        if window <= 0 or pool <= 0:
+            raise ValueError("pooled blocks lie behind a window: both sizes must be positive")
+        self.rt, self.prefix, self.width = rt, prefix, width
+        self.heads, self.kv_heads, self.dim, self.vdim = heads, kv_heads, dim, vdim
+        self.scale, self.softcap, self.window, self.pool, self.eps = float(scale), float(softcap), int(window), int(pool), float(eps)
+        self.position_encoding = position_encoding
+        self.q_size, self.k_size, self.v_size, self.inner_size = heads * dim, kv_heads * dim, kv_heads * vdim, heads * vdim
+        self.proj = Linear(rt, self.in_names(), width, self.in_sizes())
+        self.o = Linear(rt, f"{prefix}.o", self.inner_size, width)
+        self.q_b = self.k_b = self.v_b = self.q_norm_w = self.k_norm_w = self.sinks = None
+
+    def in_names(self) -> list[str]:
+        p = self.prefix
+        return [f"{p}.q", f"{p}.k", f"{p}.v"]
+
+    def in_sizes(self) -> list[int]:
+        return [self.q_size, self.k_size, self.v_size]
+
+    def children(self) -> list[Part]:
+        return [self.proj, self.o]
+
+    def param_specs(self) -> list[ParamSpec]:
+        p = self.prefix
+        return [ParamSpec(f"{p}.q.b", (self.q_size,), "linear"), ParamSpec(f"{p}.k.b", (self.k_size,), "linear"),
+                ParamSpec(f"{p}.v.b", (self.v_size,), "linear"), ParamSpec(f"{p}.q.norm", (self.q_size,), "norm"),
+                ParamSpec(f"{p}.k.norm", (self.k_size,), "norm"), ParamSpec(f"{p}.sink", (self.heads,), "linear")]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        p = self.prefix
+        f = lambda n: get(f"{p}.{n}").to(torch.float32).contiguous()
+        self.q_b, self.k_b, self.v_b = f("q.b"), f("k.b"), f("v.b")
+        self.q_norm_w, self.k_norm_w, self.sinks = f("q.norm"), f("k.norm"), f("sink")
+
+    def cache_request(self) -> tuple:
+        """(pages of the tokens inside the window, or of a block that is not complete yet; pages of the blocks' means)."""
+        v = self.vdim if self.vdim != self.dim else 0
+        return (KVPages(self.kv_heads, self.dim, max(self.window, self.pool), v_head_dim=v),
+                KVPages(self.kv_heads, self.dim, 0, v_head_dim=v, every=self.pool))
+
+    def inner(self, pre: torch.Tensor, step: StepContext, cache: tuple, out: torch.Tensor, out_scale: float = 1.0,
+              write_cache: bool = True) -> None:
+        """pre: float32 [T, >= sum(in_sizes())], the columns q | k | v of this mixer, which are changed in place; out:
+        [T, inner_size] in the activation type (contiguous) receives the heads."""
+        if not write_cache:
+            raise ops.KernelError("attention with pooled blocks writes the cache it reads")
+        if out_scale != 1.0 or not out.is_contiguous():
+            raise ops.KernelError("attention with pooled blocks writes unscaled heads into a matrix of their own")
+        rt = self.rt
+        near, far = cache
+        T, H, G, D, V = pre.shape[0], self.heads, self.kv_heads, self.dim, self.vdim
+        c1, c2, c3 = self.q_size, self.q_size + self.k_size, self.q_size + self.k_size + self.v_size
+        ops.bias_rmsnorm_cols(pre, [(0, self.q_size, self.q_b, self.q_norm_w), (c1, self.k_size, self.k_b, self.k_norm_w),
+                                    (c2, self.v_size, self.v_b, None)], self.eps, rt.stream)
+        rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
+        inv_freq, rot = rotary if rotary is not None else (None, 0)
+        table, far_table = step.block_tables[near.group], step.block_tables[far.group]
+        q = rt.empty((T, H, D))
+        ops.rope_kv(pre[:, :c1], pre[:, c1:c2], pre[:, c2:c3], q, step.positions, H, G, D, 0.0, rt.stream, inv_freq=inv_freq, rot_dim=rot,
+                    k_cache=near.k, v_cache=near.v, token_seq=step.token_seq, block_table=table, page_size=near.page_size, v_dim=V)
+        ops.pool_kv(near.k, near.v, table, far.k, far.v, far_table, step, G, D, V, near.page_size, self.pool, rt.stream)
+        ops.attention_plain(q, out.view(T, H, V), near.k, near.v, step.positions, step.token_seq, table, H, G, D, near.page_size,
+                            self.window, self.scale, rt.stream, v_dim=V, softcap=self.softcap, sinks=self.sinks, pool=self.pool,
+                            pool_k=far.k, pool_v=far.v, pool_table=far_table)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache: tuple, write_cache: bool = True) -> torch.Tensor:
+        pre = self.proj.forward(h, out_dtype=torch.float32)
+        inner = self.rt.empty((h.shape[0], self.inner_size))
+        self.inner(pre, step, cache, inner, 1.0, write_cache)
+        return self.o.forward(inner, out_dtype=torch.float32)

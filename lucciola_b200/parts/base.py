@@ -50,6 +50,8 @@ class KVPages:
     window: int = 0                 # 0: all keys; W: the last W keys (the query's own included)
     shared: bool = False            # True: one vector a token serves as key and as value (a latent); half the memory
     v_head_dim: int = 0             # size of a value head when it is not head_dim (0: the same)
+    every: int = 1                  # P > 1: one entry for every P tokens (what a mixer keeps of whole blocks of tokens):
+                                    # entry b stands at place b of the block table, and a sequence of n tokens has n // P
 
 
 @dataclass(frozen=True)

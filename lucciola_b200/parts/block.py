@@ -55,7 +55,9 @@ class PreNormBlock(Block):
 class ParallelBlock(Block):
     """One norm, two sublayers side by side: h = norm(r); r += mixer(u) + ffn(h), where the mixer reads
     u = input_taps(h) (a short causal convolution over time added to h) if the block has one, else h.  The
-    feed-forward always reads h; a block may have none.
+    feed-forward always reads h; a block may have none.  With `ffn_norm` the feed-forward has a norm of its own on the
+    same stream, r += mixer(norm(r)) + ffn(ffn_norm(r)); two RMS norms with one eps then run as one kernel that adds what
+    the block before left, norms once and applies both weights (RMSNorm.add_forward_pair).
 
     The block hands its two outputs on unsummed when the norm that follows takes them (`delta_parts`): that norm adds
     both to the 32-bit residual stream in the pass in which it reads it.  The taps' state (the last inputs of each
@@ -64,18 +66,24 @@ class ParallelBlock(Block):
     offers_delta_parts = True
 
     def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], norm: Norm, act_dtype: torch.dtype,
-                 input_taps: Optional[CausalTaps] = None):
+                 input_taps: Optional[CausalTaps] = None, ffn_norm: Optional[Norm] = None):
         self.mixer, self.feed_forward, self.norm, self.input_taps = mixer, feed_forward, norm, input_taps
+        if ffn_norm is not None and feed_forward is None:
+            raise ValueError("a norm for a feed-forward that is not there")
+        self.ffn_norm = ffn_norm
+        # two RMS norms of one stream with one eps: one kernel adds the deltas, norms once and applies both weights
+        self._paired = hasattr(norm, "add_forward_pair") and (ffn_norm is None or (type(ffn_norm) is type(norm)
+                                                               and ffn_norm.eps == norm.eps and ffn_norm.size == norm.size))
         self.act_dtype = act_dtype
         self._taps_state = input_taps.cache_request() if input_taps is not None else None
         self._rt = norm.rt
 
     @property
     def takes_delta_parts(self) -> bool:
-        return self.norm.takes_delta_parts
+        return self.norm.takes_delta_parts or (self.ffn_norm is not None and self._paired)
 
     def children(self) -> list[Part]:
-        return [p for p in (self.norm, self.input_taps, self.mixer, self.feed_forward) if p is not None]
+        return [p for p in (self.norm, self.ffn_norm, self.input_taps, self.mixer, self.feed_forward) if p is not None]
 
     def cache_request(self):
         mixer = self.mixer.cache_request()
@@ -83,13 +91,18 @@ class ParallelBlock(Block):
 
     def forward(self, residual: torch.Tensor, delta, step: StepContext, cache, write_cache: bool = True,
                 delta_parts: bool = False):
-        h = self.norm.add_forward(residual, delta, self.act_dtype)
+        if self.ffn_norm is not None and self._paired:
+            deltas = delta if isinstance(delta, tuple) else ((delta,) if delta is not None else ())
+            h, h_ffn = self.norm.add_forward_pair(residual, deltas, self.ffn_norm, self.act_dtype)
+        else:
+            h = self.norm.add_forward(residual, delta, self.act_dtype)
+            h_ffn = self.ffn_norm.forward(residual, self.act_dtype) if self.ffn_norm is not None else h
         taps_cache, mixer_cache = cache if self._taps_state is not None else (None, cache)
         u = self.input_taps.forward(h, step, taps_cache) if self.input_taps is not None else h
         a = self.mixer.forward(u, step, mixer_cache, write_cache)
         if self.feed_forward is None:
             return residual, a
-        b = self.feed_forward.forward(h, step)
+        b = self.feed_forward.forward(h_ffn, step)
         if delta_parts:
             return residual, (a, b)
         # the norm that follows adds one delta only: the mixer's output goes into the residual stream here

@@ -7,6 +7,7 @@ GatedFeedForward takes the three tensor names and the activation; SwiGLUFeedForw
 tensor names of the Qwen3 checkpoints."""
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -77,3 +78,44 @@ class SwiGLUFeedForward(GatedFeedForward):
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, intermediate_size: int):
         super().__init__(rt, f"{prefix}.gate_proj.weight", f"{prefix}.up_proj.weight", f"{prefix}.down_proj.weight",
                          hidden_size, intermediate_size, "silu")
+
+
+class DenseFeedForward(FeedForward):
+    """A feed-forward without a gate: down( act(up(h)) ).  `act` is one of ops.PLAIN_ACTS; xIELU,
+
+        z > 0: softplus(p) z^2 + z / 2        z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2,
+
+    takes its two learned numbers (p, q) from the tensor `act_name` [2]; the two positive factors are formed once, when
+    the weights are bound."""
+    recordable = True
+
+    def __init__(self, rt: Runtime, up_name: str, down_name: str, hidden_size: int, intermediate_size: int, act: str = "xielu",
+                 act_name: Optional[str] = None, out_dtype: Optional[torch.dtype] = None):
+        if act not in ops.PLAIN_ACTS:
+            raise ValueError(f"activation {act!r} of a dense feed-forward is not one of {sorted(ops.PLAIN_ACTS)}")
+        if (act == "xielu") != (act_name is not None):
+            raise ValueError("xielu, and only xielu, takes a tensor with its two numbers")
+        self.rt, self.act, self.act_name, self.out_dtype = rt, act, act_name, out_dtype
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.up = Linear(rt, up_name, hidden_size, intermediate_size)
+        self.down = Linear(rt, down_name, intermediate_size, hidden_size)
+        self.p0 = self.p1 = 0.0
+
+    def children(self) -> list[Part]:
+        return [self.up, self.down]
+
+    def param_specs(self):
+        from .base import ParamSpec
+        return [ParamSpec(self.act_name, (2,), "linear")] if self.act_name is not None else []
+
+    def bind(self, get) -> None:
+        if self.act_name is not None:
+            p, q = get(self.act_name).to(torch.float64).cpu().tolist()
+            sp = lambda x: max(x, 0.0) + math.log1p(math.exp(-abs(x)))
+            self.p0, self.p1 = sp(p), 0.5 + sp(q)
+
+    def forward(self, h, step: StepContext):
+        u = self.up.forward(h)
+        a = self.rt.empty(u.shape)
+        ops.activation(a, u, self.act, self.rt.stream, self.p0, self.p1)
+        return self.down.forward(a, out_dtype=self.out_dtype)

@@ -43,6 +43,18 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(out, residual, delta, self.weight, self.eps, self.rt.stream, rows=rows)
         return out
 
+    def add_forward_pair(self, residual: torch.Tensor, deltas: tuple, other: Optional["RMSNorm"], out_dtype: torch.dtype):
+        """residual += the deltas (none, one or two tensors); returns (this norm of the new residual, `other`'s norm of it,
+        or None without `other`): two norms of one stream share the row's root mean square when their eps agree, and one
+        kernel adds, norms and applies both weights."""
+        if other is not None and (other.size != self.size or other.eps != self.eps):
+            raise ValueError("two norms of one stream in one pass need one size and one eps")
+        a = self.rt.empty(residual.shape, out_dtype)
+        b = self.rt.empty(residual.shape, out_dtype) if other is not None else None
+        ops.add_rmsnorm_pair(a, b, residual, tuple(deltas), self.weight, other.weight if other is not None else None, self.eps,
+                             self.rt.stream)
+        return a, b
+
 
 class GroupRMSNorm(Norm):
     """y = concat_g( x_g / sqrt(mean(x_g^2) + eps) ) * w over `groups` equal consecutive parts x_g of the row.

@@ -14,6 +14,7 @@ from typing import Callable, Hashable, Optional
 
 import torch
 
+from .. import ops
 from .base import BatchShape, Mixer, ParamSpec, Part, Runtime, StepContext, StepPlan
 from .linear import Linear
 
@@ -65,3 +66,77 @@ class SideBySideMixer(Mixer):
         self.left.inner(pre[:, :self.n_left], step, left_cache, inner[:, :kl], self.left_scale, write_cache)
         self.right.inner(pre[:, self.n_left:], step, right_cache, inner[:, kl:], self.right_scale, write_cache)
         return self.o.forward(inner, out_dtype=torch.float32)
+
+
+class NormedPairMixer(Mixer):
+    """Two mixers side by side whose outputs are normed before they are added:
+
+        out = a * rmsnorm(left(x)) * w_l + b * rmsnorm(right(x)) * w_r          (norms over the model width, plain weights)
+
+    A norm does not commute with the output products, so unlike SideBySideMixer each mixer keeps its own output product
+    (32-bit sums, never rounded before the norm); what is shared is the INPUT product, one over the rows of both, and
+    one kernel norms both outputs and adds them.  Each mixer's cache request is a tuple; the pair asks for the two laid
+    end to end and hands each mixer its share."""
+
+    def __init__(self, rt: Runtime, width: int, left: Mixer, right: Mixer, left_norm_name: str, right_norm_name: str,
+                 left_scale: float, right_scale: float, eps: float):
+        for m in (left, right):
+            if not all(hasattr(m, a) for a in ("in_names", "in_sizes", "inner", "inner_size", "o")):
+                raise ValueError(f"{type(m).__name__} does not offer its steps apart (in_names, in_sizes, inner, inner_size, o)")
+        self.rt, self.width, self.eps = rt, width, float(eps)
+        self.left, self.right = left, right
+        self.left_scale, self.right_scale = float(left_scale), float(right_scale)
+        self.names = (left_norm_name, right_norm_name)
+        self.n_left = sum(left.in_sizes())
+        self.proj = Linear(rt, left.in_names() + right.in_names(), width, left.in_sizes() + right.in_sizes())
+        self._n_left_caches = len(self._as_tuple(left.cache_request()))
+        self.w_left: torch.Tensor | None = None
+        self.w_right: torch.Tensor | None = None
+
+    @staticmethod
+    def _as_tuple(r) -> tuple:
+        return r if isinstance(r, tuple) else (r,)
+
+    @property
+    def recordable(self) -> bool:
+        return bool(self.left.recordable and self.right.recordable)
+
+    def children(self) -> list[Part]:
+        # the mixers' own children but for their input products, which this part's one product replaces
+        own = [c for m in (self.left, self.right) for c in m.children() if c is not getattr(m, "proj", None)]
+        return [self.proj, *own]
+
+    def param_specs(self) -> list[ParamSpec]:
+        return (list(self.left.param_specs()) + list(self.right.param_specs())
+                + [ParamSpec(self.names[0], (self.width,), "norm"), ParamSpec(self.names[1], (self.width,), "norm")])
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        self.left.bind(get)
+        self.right.bind(get)
+        self.w_left = get(self.names[0]).to(torch.float32).contiguous()
+        self.w_right = get(self.names[1]).to(torch.float32).contiguous()
+
+    def cache_request(self) -> tuple:
+        return self._as_tuple(self.left.cache_request()) + self._as_tuple(self.right.cache_request())
+
+    def plan_key(self) -> Optional[Hashable]:
+        a, b = self.left.plan_key(), self.right.plan_key()
+        if a is not None and b is not None and a != b:
+            raise NotImplementedError("two mixers side by side that both plan work on the host")
+        return a if a is not None else b
+
+    def plan(self, batch: BatchShape) -> Optional[StepPlan]:
+        return (self.left if self.left.plan_key() is not None else self.right).plan(batch)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache, write_cache: bool = True) -> torch.Tensor:
+        left_cache, right_cache = cache[:self._n_left_caches], cache[self._n_left_caches:]
+        pre = self.proj.forward(h, out_dtype=torch.float32)
+        T = h.shape[0]
+        a_in, b_in = self.rt.empty((T, self.left.inner_size)), self.rt.empty((T, self.right.inner_size))
+        self.left.inner(pre[:, :self.n_left], step, left_cache, a_in, 1.0, write_cache)
+        self.right.inner(pre[:, self.n_left:], step, right_cache, b_in, 1.0, write_cache)
+        a = self.left.o.forward(a_in, out_dtype=torch.float32)
+        b = self.right.o.forward(b_in, out_dtype=torch.float32)
+        out = self.rt.empty((T, self.width), torch.float32)
+        ops.rmsnorm_mix2(out, a, b, self.w_left, self.w_right, self.left_scale, self.right_scale, self.eps, self.rt.stream)
+        return out
