@@ -13,7 +13,15 @@ from __future__ import annotations
 import math
 
 import torch
-import torch.nn.functional as F
+
+
+# Where an engine that serves in 16 bits may round: the inputs of products and what a cache holds.  None: nowhere (this
+# file's own arithmetic is exact to its type); the tests set it to see what such rounding alone does to a model's logits.
+ROUND = None
+
+
+def _r(x: torch.Tensor) -> torch.Tensor:
+    return x if ROUND is None else ROUND(x)
 
 
 def rms_norm(x: torch.Tensor, weight, eps: float) -> torch.Tensor:
@@ -57,6 +65,7 @@ def gated_delta_rule(h: torch.Tensor, w: dict, m: dict, eps: float, past):
     A_log, dt_bias, g, norm, o.  past: (conv inputs of q, k, v, state [heads, dim, vdim]) or None."""
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
+    h = _r(h)
     cq, ck, cv, S = past if past is not None else (None, None, None, torch.zeros(H, D, V, dtype=h.dtype))
     q, cq = short_conv(h @ w["q"].T, w["q.conv"], None, cq)
     k, ck = short_conv(h @ w["k"].T, w["k.conv"], None, ck)
@@ -77,7 +86,7 @@ def gated_delta_rule(h: torch.Tensor, w: dict, m: dict, eps: float, past):
             S[hd] = S[hd] + torch.outer(kk, u)
             o[t, hd] = S[hd].T @ qq
     o = rms_norm(o, w["norm"], eps) * silu(h @ w["g"].T).reshape(T, H, V)
-    return o.reshape(T, H * V) @ w["o"].T, (cq, ck, cv, S)
+    return _r(o.reshape(T, H * V)) @ w["o"].T, (cq, ck, cv, S)
 
 
 def rotate_half(x: torch.Tensor, positions: torch.Tensor, dims: int, base: float) -> torch.Tensor:
@@ -99,11 +108,13 @@ def pooled_window_attention(h: torch.Tensor, w: dict, m: dict, eps: float, past)
     T = h.shape[0]
     start = 0 if past is None else past[0].shape[0]
     pos = torch.arange(start, start + T)
+    h = _r(h)
     q = rms_norm(h @ w["q"].T + w["q.b"], w["q.norm"], eps).reshape(T, H, D)
     k = rms_norm(h @ w["k"].T + w["k.b"], w["k.norm"], eps).reshape(T, G, D)
     v = (h @ w["v"].T + w["v.b"]).reshape(T, G, V)
     q = rotate_half(q, pos, m["rot"]["dims"], m["rot"]["base"])
     k = rotate_half(k, pos, m["rot"]["dims"], m["rot"]["base"])
+    q, k, v = _r(q), _r(k), _r(v)                               # as the cache holds them
     if past is not None:
         k, v = torch.cat([past[0], k], dim=0), torch.cat([past[1], v], dim=0)
     cap = m["softcap"]
@@ -122,7 +133,7 @@ def pooled_window_attention(h: torch.Tensor, w: dict, m: dict, eps: float, past)
             mx = torch.maximum(s.max(), w["sink"][hd])
             e = torch.exp(s - mx)
             out[t, hd] = (e[:, None] * vals).sum(dim=0) / (e.sum() + torch.exp(w["sink"][hd] - mx))
-    return out.reshape(T, H * V) @ w["o"].T, (k, v)
+    return _r(out.reshape(T, H * V)) @ w["o"].T, (k, v)
 
 
 def mamba2(h: torch.Tensor, w: dict, m: dict, eps: float, past):
@@ -132,7 +143,7 @@ def mamba2(h: torch.Tensor, w: dict, m: dict, eps: float, past):
     inner = H * V
     T = h.shape[0]
     conv_in, S = past if past is not None else (None, torch.zeros(H, N, V, dtype=h.dtype))
-    zxbcdt = h @ w["in"].T
+    zxbcdt = _r(h) @ w["in"].T
     z, xbc, dt = zxbcdt[:, :inner], zxbcdt[:, inner:2 * inner + 2 * G * N], zxbcdt[:, 2 * inner + 2 * G * N:]
     xbc, conv_in = short_conv(xbc, w["conv"], w["conv.b"], conv_in)
     xbc = silu(xbc)
@@ -150,7 +161,7 @@ def mamba2(h: torch.Tensor, w: dict, m: dict, eps: float, past):
             y[t, hd] = S[hd].T @ C[t, hd // per] + w["D"][hd] * x[t, hd]
     y = y.reshape(T, inner) * silu(z)
     y = (rms_norm(y.reshape(T, NG, inner // NG), None, eps)).reshape(T, inner) * w["norm"]
-    return y @ w["o"].T, (conv_in, S)
+    return _r(y) @ w["o"].T, (conv_in, S)
 
 
 def side_by_side(h: torch.Tensor, w: dict, m: dict, eps: float, past):
@@ -165,7 +176,7 @@ def side_by_side(h: torch.Tensor, w: dict, m: dict, eps: float, past):
 
 def dense_feed_forward(h: torch.Tensor, w: dict) -> torch.Tensor:
     """down( xielu(up h) ); w: up, down, act = (p, q)."""
-    return xielu(h @ w["up"].T, float(w["act"][0]), float(w["act"][1])) @ w["down"].T
+    return _r(xielu(_r(_r(h) @ w["up"].T), float(w["act"][0]), float(w["act"][1]))) @ w["down"].T
 
 
 MIXERS = {"delta": gated_delta_rule, "delta_2": gated_delta_rule, "parallel": side_by_side}
@@ -196,7 +207,7 @@ class PlainNelovik:
             x = x + a
             if layers_out is not None:
                 layers_out.append(x.clone())
-        return rms_norm(x, self.w["final.norm"], eps) @ self.w["head"].T, new_past
+        return _r(rms_norm(x, self.w["final.norm"], eps)) @ self.w["head"].T, new_past
 
     def forward(self, ids, layers_out: list | None = None) -> torch.Tensor:
         return self.run(ids, None, layers_out)[0]
