@@ -30,6 +30,9 @@ Riruzen design (parallel blocks, alternating HGRN2 and latent-attention mixers) 
 decoder of this engine at the same width, feed-forward size, head count and depth; one JSON line a (size, model), random weights.
 `--design bonolorn` does the same for the Bonolorn design (blocks that norm a sublayer's output; windowed attention with a distance
 bias beside decay linear attention; gelu feed-forwards and routed experts in turn), beside Qwen3 and Riruzen at equal sizes.
+`--design nelovik` does the same for the Nelovik design (parallel blocks with a norm for each sublayer; layers of the gated delta
+rule and, every fourth, windowed attention with pooled blocks, capped scores and sinks beside a Mamba-2 state space; an xIELU
+feed-forward), beside Bonolorn and Qwen3 at equal sizes.
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures 6650 GB/s and 1590 TFLOP/s.  The timed work reads far more than the 126 MB of L2
@@ -436,6 +439,10 @@ DESIGN_SIZES = {
 }
 
 
+# the models a --design run measures: the design and the nearest ones beside it
+DESIGN_BESIDE = {"riruzen": ("riruzen", "qwen3"), "bonolorn": ("riruzen", "qwen3", "bonolorn"), "nelovik": ("nelovik", "bonolorn", "qwen3")}
+
+
 def design_configs(size: dict, layers: int, positions: int) -> dict:
     """The Riruzen configuration of these sizes (HGRN2 and latent attention in turn) and the Qwen3 one beside it."""
     W, H, D = size["width"], size["heads"], size["dim"]
@@ -456,7 +463,50 @@ def design_configs(size: dict, layers: int, positions: int) -> dict:
     bonolorn = {"architecture": "Bonolorn", "vocab": size["vocab"], "width": W, "residual_mult": 0.3, "norm": {"eps": 1e-5},
                 "layers": [{"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]} if i % 2 == 0 else moe}
                            for i in range(layers)]}
-    return {"riruzen": riruzen, "qwen3": qwen3, "bonolorn": bonolorn}
+    # Nelovik: three layers of the gated delta rule (heads of 128 x 128 state, half as many q/k heads; every other one with as
+    # many) and then one whose mixer is windowed attention with pooled blocks (half the heads, window 1024, blocks of 64) beside a
+    # Mamba-2 state space (heads of 64 values x 128 state); an ungated feed-forward of the size's `ff`
+    def delta(kind, kv):
+        return {"type": kind, "mixer": {"heads": H, "kv_heads": kv, "dim": D, "vdim": D, "conv": 4}, "mlp": {"kind": "dense", "ff": size["ff"]}}
+    pair = {"type": "parallel", "mlp": {"kind": "dense", "ff": size["ff"]}, "mixer": {
+        "left": {"heads": H // 2, "kv_heads": max(H // 8, 1), "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0,
+                 "rot": {"dims": D // 2, "base": 1e6}, "mask": {"size": 1024, "pool": 64}},
+        "right": {"heads": W // 64, "vdim": 64, "state": 128, "groups": 2, "norm_groups": 2, "conv": 4}}}
+    order = [delta("delta", max(H // 2, 1)), delta("delta_2", H), delta("delta", max(H // 2, 1)), pair]
+    nelovik = {"architecture": "Nelovik", "vocab": size["vocab"], "width": W, "norm": {"eps": 1e-6},
+               "layers": [order[i % 4] for i in range(layers)]}
+    return {"riruzen": riruzen, "qwen3": qwen3, "bonolorn": bonolorn, "nelovik": nelovik}
+
+
+def nelovik_costs(cfg: dict) -> dict:
+    """The same for a Nelovik configuration: the keys and values inside the window and the blocks' means behind it are what a
+    decoded token reads of a sequence (`window`, `pool`); the states and the convolutions' last inputs are read and written."""
+    W = cfg["width"]
+    weights = token_bytes = request_bytes = window = pool = 0
+    attn = []
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        if l["type"] == "parallel":
+            a, r = m["left"], m["right"]
+            inner = r["heads"] * r["vdim"]
+            conv = inner + 2 * r["groups"] * r["state"]
+            weights += (a["heads"] * a["dim"] + a["kv_heads"] * (a["dim"] + a["vdim"])) * W + W * a["heads"] * a["vdim"]
+            weights += (2 * inner + 2 * r["groups"] * r["state"] + r["heads"]) * W + W * inner
+            token_bytes += 2 * a["kv_heads"] * (a["dim"] + a["vdim"])
+            window, pool = a["mask"]["size"], a["mask"]["pool"]
+            request_bytes += 2 * 4 * r["heads"] * r["state"] * r["vdim"] + 2 * 4 * (r["conv"] - 1) * conv
+            attn.append(lambda T, a=a, r=r: a["heads"] * 2.0 * (a["dim"] + a["vdim"])
+                        * sum(min(t + 1, a["mask"]["size"]) + max(0, (t + 1 - a["mask"]["size"]) // a["mask"]["pool"]) for t in range(T))
+                        + 6.0 * T * r["heads"] * r["state"] * r["vdim"])
+        else:
+            qk, inner = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"]
+            weights += (2 * qk + 2 * inner + 2 * m["heads"]) * W + W * inner
+            request_bytes += 2 * 4 * m["heads"] * m["dim"] * m["vdim"] + 2 * 4 * (m["conv"] - 1) * (2 * qk + inner)
+            attn.append(lambda T, m=m: 10.0 * T * m["heads"] * m["dim"] * m["vdim"])
+        if l["mlp"]:
+            weights += 2 * l["mlp"]["ff"] * W
+    return {"weight_bytes": 2 * (weights + cfg["vocab"] * W), "token_bytes": token_bytes, "request_bytes": request_bytes,
+            "flops_per_token": 2.0 * weights, "attn_flops": lambda T: sum(f(T) for f in attn), "window": window, "pool": pool}
 
 
 def bonolorn_costs(cfg: dict) -> dict:
@@ -493,6 +543,8 @@ def design_costs(name: str, cfg: dict) -> dict:
     """Weights a decode step reads, cache bytes a cached token and a live request cost a step, FLOPs of the products a token."""
     if name == "bonolorn":
         return bonolorn_costs(cfg)
+    if name == "nelovik":
+        return nelovik_costs(cfg)
     if name == "qwen3":
         L = cfg["num_hidden_layers"]
         per_layer, weight_bytes, kv = model_bytes_and_flops(cfg, L)
@@ -544,7 +596,7 @@ def run_design(args) -> int:
         for mname, cfg in design_configs(DESIGN_SIZES[sname], layers, max(ctx, T) + K + Wm + 64).items():
             if args.design_models and mname not in args.design_models.split(","):
                 continue
-            if mname == "bonolorn" and args.design != "bonolorn":
+            if not args.design_models and mname not in DESIGN_BESIDE[args.design]:
                 continue
             cost = design_costs(mname, cfg)
             V = cfg.get("vocab", cfg.get("vocab_size"))
@@ -604,6 +656,8 @@ def run_design(args) -> int:
                 ms = a.elapsed_time(b) / steps
                 mean_ctx = sum(runner.length(r) for r in rids) / B - steps / 2
                 seen = min(mean_ctx, cost["window"]) if cost.get("window") else mean_ctx          # a window bounds the keys a step reads
+                if cost.get("pool"):                                                            # one entry a whole block behind it
+                    seen += max(0.0, mean_ctx - cost["window"]) // cost["pool"]
                 step_bytes = cost["weight_bytes"] + B * (seen * cost["token_bytes"] + cost["request_bytes"])
                 step_bytes += sum(2 * one * min(E, B * top) for one, E, top in cost.get("expert_layers", ()))
                 out[f"decode_b{B}"] = {"context": int(mean_ctx), "ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1),
@@ -650,12 +704,12 @@ def main() -> int:
     ap.add_argument("--portion", type=int, default=512, help="tokens of the portion of a --profile mixed step")
     ap.add_argument("--time-kernel", choices=["attention_key_ranges"], default=None,
                     help="time one kernel alone over a grid of sizes, print a line of JSON a case, and exit")
-    ap.add_argument("--design", choices=["riruzen", "bonolorn"], default=None,
+    ap.add_argument("--design", choices=["riruzen", "bonolorn", "nelovik"], default=None,
                     help="instead of the default workload: prefill and decode of this design beside the Qwen3 decoder at equal "
                          "sizes (--design-sizes; --layers, default 8; --prefill-tokens; --context up to 2048; --profile decode|prefill "
                          "with --batch runs one step between cudaProfilerStart/Stop)")
     ap.add_argument("--design-sizes", default="w2048,w4096", help="which of %s" % ", ".join(sorted(DESIGN_SIZES)))
-    ap.add_argument("--design-models", default="", help="which of riruzen, qwen3, bonolorn (empty: the design and those beside it)")
+    ap.add_argument("--design-models", default="", help="which of riruzen, qwen3, bonolorn, nelovik (empty: the design and those beside it)")
     args = ap.parse_args()
     if args.time_kernel == "attention_key_ranges":
         return time_attention_key_ranges()

@@ -52,6 +52,12 @@ struct FlashParams {
                                             // reads cache head j / kv_share (several groups of query heads on one cached head)
   const float* slopes;                      // optional [num_q_heads]: the score of key j for the query at position i is
   float inv_scale;                          // lowered by slopes[h] * (i - j); 1 / scale brings that into the raw score's units
+  // Three options of the kernel that fetches with 16-byte copies (the TMA kernel takes none of them):
+  float cap_raw, inv_cap_raw;               // cap_raw > 0: raw score s <- cap_raw * tanh(s * inv_cap_raw), cap_raw = softcap / scale
+  const float* sinks;                       // optional [num_q_heads]: the denominator also holds exp(sinks[h]); needs scale > 0
+  int pool;                                 // P > 0: behind the window a row at position i also sees entry b of a second paged
+  const bf16* pool_k; const bf16* pool_v;   // cache (same page size and heads) for every b with (b + 1) P - 1 <= i - window,
+  const int* pool_table; int pool_max_pages;// in the same softmax and without a distance bias
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -229,17 +235,25 @@ flash_attention_kernel(FlashParams p) {
   const int pos_last = pos0 + ntok - 1;
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
 
-  // Keys this tile can see, and the part of them this split handles (multiples of a stage).
+  // Keys this tile can see, and the part of them this split handles (multiples of a stage).  With pooled blocks the
+  // tile's keys are laid out along one axis u: first the pooled entries 0 .. nb_tile - 1 that its last row sees, padded to
+  // whole stages (PB places), then the keys lo_tile .. pos_last; a stage is all entries or all keys.
   const int lo_tile = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int span = pos_last - lo_tile + 1;
-  const int per_split = ((span + p.splits - 1) / p.splits + FA_KEYS - 1) / FA_KEYS * FA_KEYS;
-  const int kbeg = lo_tile + split * per_split;
-  const int kend = min(pos_last + 1, kbeg + per_split);      // exclusive
-  const int num_stages = kend > kbeg ? (kend - kbeg + FA_KEYS - 1) / FA_KEYS : 0;
+  const int nb_tile = (p.pool > 0 && pos_last - p.window + 1 >= p.pool) ? (pos_last - p.window + 1) / p.pool : 0;
+  const int PB = (nb_tile + FA_KEYS - 1) / FA_KEYS * FA_KEYS;
+  const int per_split = ((PB + span + p.splits - 1) / p.splits + FA_KEYS - 1) / FA_KEYS * FA_KEYS;
+  const int ubeg = split * per_split;
+  const int uend = min(PB + span, ubeg + per_split);         // exclusive
+  const int num_stages = uend > ubeg ? (uend - ubeg + FA_KEYS - 1) / FA_KEYS : 0;
+  const int kbeg = lo_tile + max(ubeg - PB, 0);              // the keys among them
+  const int kend = lo_tile + max(uend - PB, 0);              // exclusive
+  const int eend = min(nb_tile, uend);                       // the pooled entries among them end here
+  const int* pool_bt = p.pool > 0 ? p.pool_table + (size_t)seq * p.pool_max_pages : nullptr;
   // Tiles, positions and block tables were written before the step began: they are read, and the lines of the block
   // table this CTA will need are fetched, while the kernel ahead may still run.  Queries, and the keys and values that
   // kernel wrote, only after the wait.
-  if (num_stages > 0) {
+  if (kend > kbeg) {
     const int first = p.page_shift >= 0 ? (kbeg >> p.page_shift) : (kbeg / p.page_size);
     const int last = p.page_shift >= 0 ? ((kend - 1) >> p.page_shift) : ((kend - 1) / p.page_size);
     for (int i = first + tid * 32; i <= last; i += FA_THREADS * 32) asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + i));
@@ -265,22 +279,28 @@ flash_attention_kernel(FlashParams p) {
   const size_t page_stride = (size_t)(p.num_kv_heads / p.kv_share) * p.page_size * d;
   auto load_stage = [&](int stage_idx) {
     const int buf = stage_idx % STAGES;
-    const int kbase = kbeg + stage_idx * FA_KEYS + ld_row;
+    const int u0 = ubeg + stage_idx * FA_KEYS;
+    const bool pooled = u0 < PB;                 // a stage of pooled entries: the second cache through its own table
+    const int kbase = (pooled ? u0 : lo_tile + (u0 - PB)) + ld_row;
+    const int end = pooled ? eend : kend;
+    const int* tbl = pooled ? pool_bt : bt;
+    const bf16* kc = pooled ? p.pool_k : p.k_cache;
+    const bf16* vc = pooled ? p.pool_v : p.v_cache;
     int page[LOADS], slot[LOADS];
 #pragma unroll
     for (int i = 0; i < LOADS; ++i) {           // all page lookups first: they are independent loads
       const int j = kbase + i * ROW_STEP;
       const int pi = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
       slot[i] = j - pi * p.page_size;
-      page[i] = (j < kend && ld_col_valid) ? bt[pi] : -1;
+      page[i] = (j < end && ld_col_valid) ? tbl[pi] : -1;
     }
 #pragma unroll
     for (int i = 0; i < LOADS; ++i) {
       const bool valid = page[i] >= 0;
       const size_t off = valid ? (size_t)page[i] * page_stride + head_off + (size_t)slot[i] * d : 0;
       const uint32_t so = buf * TILE_BYTES + ld_smem + i * ROW_STEP * (DP * 2);
-      cp_async16(k_smem + so, p.k_cache + off, valid);
-      cp_async16(v_smem + so, p.v_cache + off, valid);
+      cp_async16(k_smem + so, kc + off, valid);
+      cp_async16(v_smem + so, vc + off, valid);
     }
   };
 
@@ -293,7 +313,7 @@ flash_attention_kernel(FlashParams p) {
   // Rows of this thread: r0 = (first row of the warp) + lane/4 and r0 + 8.
   const int warp_row0 = KEYSPLIT ? 0 : warp * 16;
   const int r0 = warp_row0 + (lane >> 2);
-  int row_pos[2], row_lo[2];
+  int row_pos[2], row_lo[2], row_nb[2]; // row_nb: how many pooled entries the row sees
   float row_bias[2];                    // the distance slope of each row's head, in the raw score's units
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -301,6 +321,7 @@ flash_attention_kernel(FlashParams p) {
     row_pos[h] = r < rows ? pos0 + r / G : -1;                  // -1: no key passes the mask
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
     row_bias[h] = (p.slopes && r < rows) ? p.slopes[kvh * G + r % G] * p.inv_scale : 0.f;
+    row_nb[h] = (p.pool > 0 && row_pos[h] - p.window + 1 >= p.pool) ? (row_pos[h] - p.window + 1) / p.pool : 0;
   }
   const bool warp_active = warp_row0 < rows;
 
@@ -330,7 +351,9 @@ flash_attention_kernel(FlashParams p) {
 
     const int buf = st % STAGES;
     const uint32_t kb = k_smem + buf * TILE_BYTES, vb = v_smem + buf * TILE_BYTES;
-    const int kbase = kbeg + st * FA_KEYS;
+    const int u0 = ubeg + st * FA_KEYS;
+    const bool pooled = u0 < PB;
+    const int kbase = pooled ? u0 : lo_tile + (u0 - PB);      // the stage's first pooled entry or key
 
     // ---- S = Q K^T: 16 rows x (64 or, with shared rows, this warp's 16) keys -----------------------
     const int key0 = KEYSPLIT ? warp * 16 : 0;       // first key of the stage this warp visits
@@ -354,17 +377,22 @@ flash_attention_kernel(FlashParams p) {
     // ---- mask, online softmax ----------------------------------------------------------------
     // Rows past the tile's last (zero queries, positions -1) need no mask of their own: what they gather is never
     // written, and it is finite, because keys and values of slots that hold nothing lie at or past kend.
-    const bool need_mask = (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend);
+    const bool need_mask = pooled || (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend);
+    const bool biased = p.slopes && !pooled;
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
-        if (need_mask || p.slopes) {
+        if (p.cap_raw > 0.f) {                              // tanh(x) = 1 - 2 / (exp(2 x) + 1), exact at both ends
+          const float ex = __expf(2.f * s[nb][e] * p.inv_cap_raw);
+          s[nb][e] = p.cap_raw * (1.f - __fdividef(2.f, ex + 1.f));
+        }
+        if (need_mask || biased) {
           const int j = kbase + key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-          s[nb][e] = fmaf(-row_bias[h], (float)(row_pos[h] - j), s[nb][e]);
-          if (need_mask && (j > row_pos[h] || j < row_lo[h] || j >= kend)) s[nb][e] = -INFINITY;
+          if (biased) s[nb][e] = fmaf(-row_bias[h], (float)(row_pos[h] - j), s[nb][e]);
+          if (pooled ? (j >= row_nb[h]) : (need_mask && (j > row_pos[h] || j < row_lo[h] || j >= kend))) s[nb][e] = -INFINITY;
         }
         m_new[h] = fmaxf(m_new[h], s[nb][e]);
       }
@@ -419,6 +447,22 @@ flash_attention_kernel(FlashParams p) {
     }
   }
   cp_async_wait<0>();
+
+  // ---- the sink: one more term of the denominator, with no key and no value; the first range's first warp adds it ----
+  if (p.sinks && split == 0 && (KEYSPLIT ? warp == 0 : warp_active)) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + 8 * h;
+      if (r >= rows) continue;
+      const float sink = p.sinks[kvh * G + r % G] * p.inv_scale;          // in the raw score's units
+      const float m_new = fmaxf(m_run[h], sink);
+      const float a = m_run[h] == -INFINITY ? 0.f : exp2f((m_run[h] - m_new) * p.scale_log2);
+      l_run[h] = l_run[h] * a + ((lane & 3) == 0 ? exp2f((sink - m_new) * p.scale_log2) : 0.f);
+#pragma unroll
+      for (int i = 0; i < DP / 8; ++i) { o[i][2 * h] *= a; o[i][2 * h + 1] *= a; }
+      m_run[h] = m_new;
+    }
+  }
 
   // ---- write: the row sums live in four lanes each ------------------------------------------------
 #pragma unroll
@@ -903,12 +947,24 @@ LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads
 // kv_share >= 1: the pools hold num_kv_heads / kv_share heads and kv head j reads pool head j / kv_share, so that
 // many query heads on one cached head can be cut into groups of at most 16 (the tiles of the decode kernels).
 // slopes (optional, float32 [nq]): a linear distance bias, score(i, j) = (q_i . k_j) * scale - slopes[h] * (i - j).
-LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                 const int* positions, const int* block_table, const void* tiles, int num_tiles,
-                                 int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
-                                 int num_pages, int window, float scale, int splits, int part_rows, float* workspace,
-                                 long long workspace_elems, int kv_share, const float* slopes, cudaStream_t stream) {
-  LB_CHECK_ARG(slopes == nullptr || scale > 0.f, "attention_flash: a distance bias needs a positive scale");
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  sinks (optional, float32 [nq]): the softmax's
+// denominator also holds exp(sinks[h]).  pool = P > 0 (needs a window): a query at position i also sees entry b of the
+// second paged cache pool_k / pool_v (same page size and heads, block table pool_table with pool_max_pages columns) for
+// every b with (b + 1) P - 1 <= i - window.  Any of the three keeps the launch off the TMA kernel.
+LB_EXPORT int lb_attention_flash_ex(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                    const int* positions, const int* block_table, const void* tiles, int num_tiles,
+                                    int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
+                                    int num_pages, int window, float scale, int splits, int part_rows, float* workspace,
+                                    long long workspace_elems, int kv_share, const float* slopes, float softcap,
+                                    const float* sinks, int pool, const void* pool_k, const void* pool_v, const int* pool_table,
+                                    int pool_max_pages, cudaStream_t stream) {
+  LB_CHECK_ARG((slopes == nullptr && sinks == nullptr && !(softcap > 0.f)) || scale > 0.f,
+               "attention_flash: a distance bias, a cap and a sink need a positive scale");
+  LB_CHECK_ARG(softcap >= 0.f, "attention_flash: a cap of %f", (double)softcap);
+  LB_CHECK_ARG(pool == 0 || (pool > 0 && window > 0 && pool_k && pool_v && pool_table && pool_max_pages > 0 && kv_share == 1 &&
+                             ((uintptr_t)pool_k % 16 == 0) && ((uintptr_t)pool_v % 16 == 0)),
+               "attention_flash: pooled blocks need a window, the pooled cache and its block table");
+  if (softcap > 0.f || sinks || pool > 0) num_pages = 0;
   LB_CHECK_ARG(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
                "attention_flash: %d query heads are not a multiple of %d kv heads", num_q_heads, num_kv_heads);
   LB_CHECK_ARG(kv_share >= 1 && num_kv_heads % kv_share == 0, "attention_flash: %d kv heads cannot share cached heads %d by %d",
@@ -945,7 +1001,10 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   p.page_shift = page_shift;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.kv_share = kv_share;
-  p.slopes = slopes; p.inv_scale = slopes ? 1.f / scale : 0.f;
+  p.slopes = slopes; p.inv_scale = (slopes || sinks) ? 1.f / scale : 0.f;
+  p.cap_raw = softcap > 0.f ? softcap / scale : 0.f; p.inv_cap_raw = softcap > 0.f ? scale / softcap : 0.f;
+  p.sinks = sinks; p.pool = pool; p.pool_k = (const lb::bf16*)pool_k; p.pool_v = (const lb::bf16*)pool_v;
+  p.pool_table = pool_table; p.pool_max_pages = pool_max_pages;
   dim3 grid(num_tiles, num_kv_heads, splits);
   const int dp = head_dim <= 64 ? 64 : 128;
   const int smem = part_rows <= 16 ? (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2   // query tile + 3 stages
@@ -1025,4 +1084,14 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
     LB_CHECK_LAUNCH("attention_flash combine");
   }
   return 0;
+}
+
+LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                 const int* positions, const int* block_table, const void* tiles, int num_tiles,
+                                 int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
+                                 int num_pages, int window, float scale, int splits, int part_rows, float* workspace,
+                                 long long workspace_elems, int kv_share, const float* slopes, cudaStream_t stream) {
+  return lb_attention_flash_ex(q, out, k_cache, v_cache, positions, block_table, tiles, num_tiles, num_q_heads, num_kv_heads,
+                               head_dim, page_size, max_pages, num_pages, window, scale, splits, part_rows, workspace,
+                               workspace_elems, kv_share, slopes, 0.f, nullptr, 0, nullptr, nullptr, nullptr, 0, stream);
 }

@@ -97,6 +97,9 @@ _SIGNATURES = {
     "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
+    "lb_attention_flash_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p,
+                              c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -1001,14 +1004,24 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                     positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, max_rows: int,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
                     splits: int, stream: int, force_workspace: bool = False, tma: bool = True, kv_share: int = 1,
-                    slopes: torch.Tensor | None = None) -> None:
+                    slopes: torch.Tensor | None = None, softcap: float = 0.0, sinks: torch.Tensor | None = None, pool: int = 0,
+                    pool_k: torch.Tensor | None = None, pool_v: torch.Tensor | None = None,
+                    pool_table: torch.Tensor | None = None) -> None:
     """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0).
     `kv_share` > 1: the pools hold num_kv_heads / kv_share heads, and kv head j of this call reads pool head j // kv_share
     (many query heads on one cached head, cut into groups of at most 16 so that decoded tokens fit the decode kernel's tiles).
     `force_workspace` sends the partial results of the splits through the workspace and the combining
     kernel even where a cluster could combine them.  Tiles of at most 16 query rows (decoded tokens) over pages of
     8 to 128 tokens run in the kernel whose keys and values a warp of its own fetches by TMA; `tma=False` keeps them
-    in the kernel that fetches with 16-byte copies, which takes every page size."""
+    in the kernel that fetches with 16-byte copies, which takes every page size.  `softcap`, `sinks` and `pool` (with
+    pool_k, pool_v, pool_table) as in attention_plain; a launch with any of them runs in the kernel with 16-byte copies."""
+    if softcap > 0 or sinks is not None or pool:
+        tma = False
+    if sinks is not None:
+        _check(sinks, "sinks", torch.float32)
+    if pool:
+        _check(pool_k, "pooled k", torch.bfloat16); _check(pool_v, "pooled v", torch.bfloat16)
+        _check(pool_table, "pooled block table", torch.int32)
     _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
     _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
     _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)
@@ -1021,10 +1034,12 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         ws_elems = n * num_kv_heads * splits * max_rows * (head_dim + 2)
         ws = _attention_workspace(q.device, ws_elems)
         ws_elems = ws.numel()
-    _call("lb_attention_flash", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+    _call("lb_attention_flash_ex", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), n, num_q_heads, num_kv_heads, head_dim,
           page_size, block_table.shape[1], k_cache.shape[0] if tma else 0, window, scale,
-          -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, kv_share, _ptr(slopes), stream)
+          -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, kv_share, _ptr(slopes), softcap, _ptr(sinks),
+          pool, _ptr(pool_k) if pool else None, _ptr(pool_v) if pool else None, _ptr(pool_table) if pool else None,
+          pool_table.shape[1] if pool else 0, stream)
 
 
 def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
@@ -1081,27 +1096,36 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
               num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-              stream: int, plan=None, kv_share: int = 1, v_dim: int = 0, slopes: torch.Tensor | None = None) -> None:
+              stream: int, plan=None, kv_share: int = 1, v_dim: int = 0, slopes: torch.Tensor | None = None,
+              softcap: float = 0.0, sinks: torch.Tensor | None = None, pool: int = 0, pool_k: torch.Tensor | None = None,
+              pool_v: torch.Tensor | None = None, pool_group: int = -1) -> None:
     """Causal attention of this step's queries over the pages of their requests.  With a `plan` (tile lists
     by kind on the device, see parts/attention.py) the tensor-core kernels run where their conditions hold:
     portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
     sizes) to the mma.sync kernels; everything else, and every step without a plan, goes to the plain kernel.
     `kv_share` > 1: the plan's lists other than "big" were made for groups of num_q_heads / (num_kv_heads * kv_share)
-    query heads, kv_share of which read one cached head (see attention_flash)."""
-    if (plan is None or (v_dim and v_dim != head_dim) or (slopes is not None and not scale > 0)
-            or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim)):
+    query heads, kv_share of which read one cached head (see attention_flash).  A capped score (`softcap`), sinks and
+    pooled blocks behind the window (`pool` tokens a block, their means in pool_k / pool_v, pages of group `pool_group`)
+    run in the mma.sync kernel with 16-byte copies, for portions and for decoded tokens, or in the plain kernel."""
+    extras = softcap > 0 or sinks is not None or pool > 0
+    pool_table = step.block_tables[pool_group] if pool else None
+    if (plan is None or (v_dim and v_dim != head_dim) or ((slopes is not None or extras) and not scale > 0)
+            or (pool and kv_share != 1) or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim)):
         # value heads of another size than the keys' are the plain kernel's alone
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
-                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream, v_dim=v_dim, slopes=slopes)
+                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream, v_dim=v_dim, slopes=slopes,
+                        softcap=softcap, sinks=sinks, pool=pool, pool_k=pool_k, pool_v=pool_v, pool_table=pool_table)
         return
     meta, most_rows = plan.arrays, plan.host["rows"]
     longest = step.span_hint or step.max_context_len                 # a recorded step plans for a bucket of lengths
     span = min(longest, window + step.max_q_len) if window > 0 else longest
+    if pool:
+        span += -(-max(longest - window, 0) // pool)                 # one entry a block behind the window
     kinds = ["all"]
     if slopes is not None:
         _check(slopes, "distance slopes", torch.float32)
-    if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
-                                              step.block_tables[group].shape[1]):
+    if not extras and "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
+                                                             step.block_tables[group].shape[1]):
         attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"],
                           num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream,
                           key_splits=attention_tcgen05_splits(meta["big"].shape[0], num_kv_heads, span), slopes=slopes)
@@ -1109,8 +1133,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     for kind in kinds:
         tiles = meta[kind]
         rows = min(most_rows[kind], 64)
-        wide = attention_wide_clusters(head_dim) if rows <= 16 and page_size in (8, 16, 32, 64, 128) else 0
+        wide = attention_wide_clusters(head_dim) if rows <= 16 and page_size in (8, 16, 32, 64, 128) and not extras else 0
         splits = attention_splits(tiles.shape[0], num_kv_heads * kv_share, span, rows, wide_clusters=wide)
         attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, rows,
                         num_q_heads, num_kv_heads * kv_share, head_dim, page_size, window, scale, splits, stream, kv_share=kv_share,
-                        slopes=slopes)
+                        slopes=slopes, softcap=softcap, sinks=sinks, pool=pool, pool_k=pool_k, pool_v=pool_v, pool_table=pool_table)

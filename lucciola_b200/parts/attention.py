@@ -339,6 +339,21 @@ class PooledWindowAttention(Mixer):
         self.q_b, self.k_b, self.v_b = f("q.b"), f("k.b"), f("v.b")
         self.q_norm_w, self.k_norm_w, self.sinks = f("q.norm"), f("k.norm"), f("sink")
 
+    def plan_key(self) -> Optional[Hashable]:
+        """The tile lists of the tensor-core kernels, as GQAttention's: they depend on the group size alone."""
+        g = self.heads // self.kv_heads
+        return ("attention tiles", g) if self.rt.fast_kernels and g <= TILE_ROWS and self.vdim == self.dim else None
+
+    def plan(self, batch: BatchShape) -> Optional[StepPlan]:
+        g = self.heads // self.kv_heads
+        if batch.max_q_len == 1:
+            key = (g, len(batch.q_lens))
+            hit = GQAttention._decode_plans.get(key)
+            if hit is None:
+                hit = GQAttention._decode_plans[key] = plan_tiles(batch, g)
+            return hit
+        return plan_tiles(batch, g)
+
     def cache_request(self) -> tuple:
         """(pages of the tokens inside the window, or of a block that is not complete yet; pages of the blocks' means)."""
         v = self.vdim if self.vdim != self.dim else 0
@@ -366,9 +381,9 @@ class PooledWindowAttention(Mixer):
         ops.rope_kv(pre[:, :c1], pre[:, c1:c2], pre[:, c2:c3], q, step.positions, H, G, D, 0.0, rt.stream, inv_freq=inv_freq, rot_dim=rot,
                     k_cache=near.k, v_cache=near.v, token_seq=step.token_seq, block_table=table, page_size=near.page_size, v_dim=V)
         ops.pool_kv(near.k, near.v, table, far.k, far.v, far_table, step, G, D, V, near.page_size, self.pool, rt.stream)
-        ops.attention_plain(q, out.view(T, H, V), near.k, near.v, step.positions, step.token_seq, table, H, G, D, near.page_size,
-                            self.window, self.scale, rt.stream, v_dim=V, softcap=self.softcap, sinks=self.sinks, pool=self.pool,
-                            pool_k=far.k, pool_v=far.v, pool_table=far_table)
+        ops.attention(q, out.view(T, H, V), near.k, near.v, step, near.group, H, G, D, near.page_size, self.window, self.scale,
+                      rt.stream, plan=step.plans.get(self.plan_key()), v_dim=V if V != D else 0, softcap=self.softcap,
+                      sinks=self.sinks, pool=self.pool, pool_k=far.k, pool_v=far.v, pool_group=far.group)
 
     def forward(self, h: torch.Tensor, step: StepContext, cache: tuple, write_cache: bool = True) -> torch.Tensor:
         pre = self.proj.forward(h, out_dtype=torch.float32)

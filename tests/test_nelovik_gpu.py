@@ -215,7 +215,8 @@ def test_bias_and_norm_over_whole_projections():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv,dim,vdim,page,window,pool", [(3, 1, 20, 12, 8, 24, 5), (4, 2, 64, 64, 16, 40, 16), (2, 2, 32, 80, 4, 7, 3),
-                                                               (8, 2, 128, 128, 16, 33, 32), (1, 1, 16, 16, 8, 1, 1), (2, 1, 24, 24, 16, 6, 9)])
+                                                               (8, 2, 128, 128, 16, 33, 32), (1, 1, 16, 16, 8, 1, 1), (2, 1, 24, 24, 16, 6, 9),
+                                                               (4, 1, 64, 64, 16, 24, 1), (8, 8, 96, 96, 32, 70, 2), (16, 1, 32, 32, 8, 12, 4)])
 def test_a_query_finds_its_one_key_or_block_at_every_edge(dtype, heads, kv, dim, vdim, page, window, pool):
     """Keys and values of a long sequence in pages; what has left the window AND been pooled is overwritten with NaN.
     One key far above all others stands in turn just inside the window, just outside it (in a block not yet complete or
@@ -250,32 +251,60 @@ def test_a_query_finds_its_one_key_or_block_at_every_edge(dtype, heads, kv, dim,
         for start, count in ((0, n - 9), (n - 9, 6), (n - 3, 1), (n - 2, 1), (n - 1, 1)):
             step = batch_of([count], [0], [start])
             ops.pool_kv(kc, vc, table, fk, fv, far_table, step, kv, dim, vdim, page, pool, stream())
-        keep_from = (n - 3) - max(window, pool) + 1                                                         # what the window group still holds
+        longest = min(37, n - 1)
+        keep_from = (n - longest) - max(window, pool) + 1                                                   # what the window group still holds
         if keep_from > 0:
             gone = torch.arange(0, keep_from, device=DEV)
             gone = gone[(gone // page) < (keep_from // page)]                                                 # whole pages only
             kc[table[0, gone // page].long(), :, gone % page] = float("nan")
             vc[table[0, gone // page].long(), :, gone % page] = float("nan")
         Kc, Vc = K.to(dtype).double(), V.to(dtype).double()
-        for qs, starts in (([1], [last]), ([3], [n - 3])):
-            step = batch_of(qs, [0], starts)
-            qq = q[-qs[0]:].to(dtype).contiguous()
-            out = torch.empty(qs[0], heads, vdim, dtype=dtype, device=DEV)
-            ops.attention_plain(qq, out, kc, vc, step.positions, step.token_seq, table, heads, kv, dim, page, window, scale, stream(),
-                                v_dim=vdim, softcap=cap, sinks=sinks, pool=pool, pool_k=fk, pool_v=fv, pool_table=far_table)
-            for r in range(qs[0]):
-                i = starts[0] + r
-                nb, lo = max(0, (i - window + 1) // pool), max(0, i - window + 1)
-                for h in range(heads):
-                    gk = h // (heads // kv)
-                    mk = Kc[:nb * pool, gk].reshape(nb, pool, dim).mean(1).to(dtype).double()
-                    mv = Vc[:nb * pool, gk].reshape(nb, pool, vdim).mean(1).to(dtype).double()
-                    keys, vals = torch.cat([mk, Kc[lo:i + 1, gk]]), torch.cat([mv, Vc[lo:i + 1, gk]])
-                    s = cap * torch.tanh(keys @ qq[r, h].double() * scale / cap)
-                    e = torch.exp(s - s.max())
-                    want = (e[:, None] * vals).sum(0) / (e.sum() + torch.exp(sinks[h].double() - s.max()))
-                    err = (out[r, h].double() - want).abs().max().item()
-                    assert err <= (1e-5 if dtype == torch.float32 else 3e-2) * max(want.abs().max().item(), 0.3), (spot, i, h, err)
+        q = torch.cat([torch.randn(longest - 3, heads, dim, device=DEV, generator=g), q])                    # the queries of the last `longest` positions
+        two = table.repeat(2, 1).contiguous(), far_table.repeat(2, 1).contiguous()                           # two requests that read the same pages
+        fast = dtype == torch.bfloat16 and dim == vdim and ops.attention_flash_ok(q.to(dtype), heads, kv, dim)
+        for qs, starts in (([1], [last]), ([3], [n - 3]), ([longest], [n - longest]), ([1, longest], [last, n - longest]), ([2, 1, 5], [n - 2, last, n - 5])):
+            step = batch_of(qs, [0] * len(qs), starts)
+            tb, ftb = (table, far_table) if len(qs) == 1 else (two[0][:1].repeat(len(qs), 1).contiguous(), two[1][:1].repeat(len(qs), 1).contiguous())
+            qq = torch.cat([q[longest - (n - st): longest - (n - st) + c] for c, st in zip(qs, starts)]).to(dtype).contiguous()
+            outs = []
+            out = torch.empty(sum(qs), heads, vdim, dtype=dtype, device=DEV)
+            ops.attention_plain(qq, out, kc, vc, step.positions, step.token_seq, tb, heads, kv, dim, page, window, scale, stream(),
+                                v_dim=vdim, softcap=cap, sinks=sinks, pool=pool, pool_k=fk, pool_v=fv, pool_table=ftb)
+            outs.append(("plain", out))
+            if fast:
+                # the tensor-core kernel: as the engine calls it, and with its keys cut into ranges both ways of combining them
+                from lucciola_b200.parts.attention import plan_tiles
+                from lucciola_b200.parts.base import BatchShape, PlanView
+                made = plan_tiles(BatchShape(list(qs), list(starts), max(qs), n, n), heads // kv)
+                view = PlanView({k: torch.from_numpy(a).to(DEV) for k, a in made.arrays.items()}, made.host)
+                step.block_tables = [tb, ftb]
+                out = torch.full((sum(qs), heads, vdim), float("nan"), dtype=dtype, device=DEV)
+                ops.attention(qq, out, kc, vc, step, 0, heads, kv, dim, page, window, scale, stream(), plan=view, softcap=cap, sinks=sinks,
+                              pool=pool, pool_k=fk, pool_v=fv, pool_group=1)
+                outs.append(("tensor cores", out))
+                rows = min(made.host["rows"]["all"], 64)
+                for splits, ws in ((2, False), (3, True), (4, False), (5, True)):
+                    out = torch.full((sum(qs), heads, vdim), float("nan"), dtype=dtype, device=DEV)
+                    ops.attention_flash(qq, out, kc, vc, step.positions, tb, view.arrays["all"], rows, heads, kv, dim, page, window, scale,
+                                        splits, stream(), force_workspace=ws, softcap=cap, sinks=sinks, pool=pool, pool_k=fk, pool_v=fv,
+                                        pool_table=ftb)
+                    outs.append((f"tensor cores, {splits} key ranges", out))
+            r = 0
+            for c, st in zip(qs, starts):
+                for i in range(st, st + c):
+                    nb, lo = max(0, (i - window + 1) // pool), max(0, i - window + 1)
+                    for h in range(heads):
+                        gk = h // (heads // kv)
+                        mk = Kc[:nb * pool, gk].reshape(nb, pool, dim).mean(1).to(dtype).double()
+                        mv = Vc[:nb * pool, gk].reshape(nb, pool, vdim).mean(1).to(dtype).double()
+                        keys, vals = torch.cat([mk, Kc[lo:i + 1, gk]]), torch.cat([mv, Vc[lo:i + 1, gk]])
+                        sc = cap * torch.tanh(keys @ qq[r, h].double() * scale / cap)
+                        e = torch.exp(sc - sc.max())
+                        want = (e[:, None] * vals).sum(0) / (e.sum() + torch.exp(sinks[h].double() - sc.max()))
+                        for which, out in outs:
+                            err = (out[r, h].double() - want).abs().max().item()
+                            assert err <= (1e-5 if dtype == torch.float32 else 3e-2) * max(want.abs().max().item(), 0.3), (which, spot, qs, i, h, err)
+                    r += 1
 
 
 # ---- the whole model -------------------------------------------------------------------------------------------------
