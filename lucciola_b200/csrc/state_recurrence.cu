@@ -12,19 +12,23 @@
 // vectors first, x / sqrt(sum x^2 + unit_eps), and q is multiplied by q_scale.  All inputs are 32-bit rows that may
 // be column ranges of wider matrices; a, b are one number a head and token.
 //
-// A CTA takes (32 value columns, a head, a sequence) and walks the sequence's tokens of this step in order.  A
-// column of the state belongs to four neighbouring lanes, which hold its rows r = sub + 4 i in registers and add
-// their partial dot products by two shuffles; the columns never talk to one another.  The tokens' q, k, v, g, w are
-// staged through shared memory 16 tokens at a time (the unit norm and the decay are formed there, a warp a token).
-// Every sum visits its terms in an order that the sizes fix, so a result does not depend on how a sequence is cut
-// into steps or on what else the step holds.
+// A CTA of 128 threads takes (COLS value columns, a head, a sequence) and walks the sequence's tokens of this step in
+// order.  A column of the state belongs to SUB neighbouring lanes (4 for up to 64 state rows, else 8; COLS = 128 / SUB),
+// each of which holds RPL consecutive rows in registers and adds its partial dot products to its neighbours' by
+// shuffles; the columns never talk to one another.  The tokens' q, k, v and the two numbers a head are fetched 16
+// tokens at a time by cp.async into one of two buffers, the chunk after the one at work, so the walk never waits for
+// global memory; the unit norm and the decays are formed in shared memory when a chunk has landed (a warp a token).
+// Only S^T k lies on the path from one token to the next: the lanes' partial read-outs S^T q go to shared memory
+// unreduced and are added, SUB at a time, when the chunk is through, which also makes the stores of `out` whole
+// lines.  The state enters and leaves through a shared tile, in whole lines as well.  Every sum visits its terms in
+// an order that the sizes fix, so a result does not depend on how a sequence is cut into steps or on what else the
+// step holds.
 #include "common.cuh"
 
 namespace lb {
 
 constexpr int SR_TOKENS = 16;    // tokens staged at a time
-constexpr int SR_COLS = 32;      // value columns of a CTA
-constexpr int SR_SUB = 4;        // lanes that share a column
+constexpr int SR_THREADS = 128;
 
 struct StateRecurrenceParams {
   const float* q; const float* k; const float* v; const float* a; const float* b;
@@ -34,104 +38,176 @@ struct StateRecurrenceParams {
   const int* cu_tokens; const int* slots;
   int heads, groups, dim, vdim, unit_norm;
   float q_scale, unit_eps;
+  int vec;                       // q, k, v rows start on 16-byte boundaries and hold whole 16-byte pieces
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-template <bool DELTA, int RPL>
-__global__ void __launch_bounds__(SR_COLS * SR_SUB) state_recurrence_kernel(StateRecurrenceParams p) {
-  constexpr int DP = RPL * SR_SUB;                 // rows, padded
-  __shared__ float q_s[SR_TOKENS][DP];
-  __shared__ float k_s[SR_TOKENS][DP];
-  __shared__ float v_s[SR_TOKENS][SR_COLS];
-  __shared__ float g_s[SR_TOKENS], w_s[SR_TOKENS];
+__device__ __forceinline__ void sr_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void sr_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// floats of shared memory: q and k (two buffers of 16 rows of (RPL + 4) * SUB), v, a, b (two buffers), g, w, and the
+// tile that holds the lanes' partial read-outs of a chunk or, at both ends, the CTA's part of the state
+__host__ __device__ constexpr int sr_smem_floats(int rpl, int sub) {
+  const int cols = SR_THREADS / sub, row = (rpl + 4) * sub;
+  const int tile = SR_TOKENS * SR_THREADS > rpl * sub * cols ? SR_TOKENS * SR_THREADS : rpl * sub * cols;
+  return 4 * SR_TOKENS * row + 2 * SR_TOKENS * cols + 4 * SR_TOKENS + 2 * SR_TOKENS + tile;
+}
+
+template <bool DELTA, int RPL, int SUB>
+__global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecurrenceParams p) {
+  constexpr int T = SR_TOKENS, COLS = SR_THREADS / SUB, ROW = (RPL + 4) * SUB, DP = RPL * SUB;
+  extern __shared__ __align__(16) float sr_smem[];
+  float* q_s = sr_smem;                           // [2][T][ROW]: row r of a token at r + 4 * (r / RPL)
+  float* k_s = q_s + 2 * T * ROW;
+  float* v_s = k_s + 2 * T * ROW;                 // [2][T][COLS]
+  float* a_s = v_s + 2 * T * COLS;                // [2][T] as the product left them
+  float* b_s = a_s + 2 * T;
+  float* g_s = b_s + 2 * T;                       // [T] decay
+  float* w_s = g_s + T;                           // [T] write strength
+  float* o_s = w_s + T;                           // [T][COLS][SUB] partial read-outs; the state's tile [DP][COLS] at both ends
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int sub = tid % SR_SUB, col_local = tid / SR_SUB;
+  const int sub = tid % SUB, col_local = tid / SUB;
   const int h = blockIdx.y, seq = blockIdx.z;
-  const int col = blockIdx.x * SR_COLS + col_local;
-  const bool col_ok = col < p.vdim;
+  const int col0 = blockIdx.x * COLS;
   const int grp = h / (p.heads / p.groups);
   const float A = expf(p.A_log[h]), dtb = p.dt_bias[h];
   const float Dh = p.D ? p.D[h] : 0.f;
+  for (int i = tid; i < 4 * T * ROW + 2 * T * COLS; i += SR_THREADS) sr_smem[i] = 0.f;     // padding and rows past dim stay zero
   pdl_wait();
   const int first = p.cu_tokens[seq], n = p.cu_tokens[seq + 1] - first;
   float* S = p.state + ((size_t)p.slots[seq] * p.heads + h) * p.dim * p.vdim;
+  const int shift = ((32 / SUB) * sub) % COLS;     // a lane's column of the state's tile, turned so that a warp's lanes spread over the banks
 
+  // the state: whole lines into the tile, then each lane's rows into registers
+  for (int i = tid; i < DP * COLS; i += SR_THREADS) {
+    const int r = i / COLS, c = i % COLS, col = col0 + c;
+    o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS] = (r < p.dim && col < p.vdim) ? S[(size_t)r * p.vdim + col] : 0.f;
+  }
+  __syncthreads();
   float s[RPL];
 #pragma unroll
-  for (int i = 0; i < RPL; ++i) {
-    const int r = sub + SR_SUB * i;
-    s[i] = (col_ok && r < p.dim) ? S[(size_t)r * p.vdim + col] : 0.f;
-  }
+  for (int i = 0; i < RPL; ++i) s[i] = o_s[(sub * RPL + i) * COLS + (col_local + shift) % COLS];
 
-  for (int t0 = 0; t0 < n; t0 += SR_TOKENS) {
-    const int nt = min(SR_TOKENS, n - t0);
-    __syncthreads();                               // the chunk before has been read
-    for (int i = tid; i < nt * DP; i += blockDim.x) {
-      const int tt = i / DP, r = i % DP;
-      const size_t row = (size_t)(first + t0 + tt);
-      q_s[tt][r] = r < p.dim ? p.q[row * p.q_ld + (size_t)grp * p.dim + r] : 0.f;
-      k_s[tt][r] = r < p.dim ? p.k[row * p.k_ld + (size_t)grp * p.dim + r] : 0.f;
-    }
-    for (int i = tid; i < nt * SR_COLS; i += blockDim.x) {
-      const int tt = i / SR_COLS, c = blockIdx.x * SR_COLS + i % SR_COLS;
-      v_s[tt][i % SR_COLS] = c < p.vdim ? p.v[(size_t)(first + t0 + tt) * p.v_ld + (size_t)h * p.vdim + c] : 0.f;
+  auto fetch = [&](int c) {                        // chunk c into buffer c & 1
+    const int buf = c & 1, t0 = c * T, nt = min(T, n - t0);
+    float* qb = q_s + buf * T * ROW;
+    float* kb = k_s + buf * T * ROW;
+    float* vb = v_s + buf * T * COLS;
+    const size_t row0 = (size_t)(first + t0);
+    if (p.vec) {
+      const int per = p.dim / 4;
+      for (int i = tid; i < nt * per; i += SR_THREADS) {
+        const int tt = i / per, r = (i % per) * 4, dst = tt * ROW + r + 4 * (r / RPL);
+        sr_cp16(qb + dst, p.q + (row0 + tt) * p.q_ld + (size_t)grp * p.dim + r);
+        sr_cp16(kb + dst, p.k + (row0 + tt) * p.k_ld + (size_t)grp * p.dim + r);
+      }
+      for (int i = tid; i < nt * (COLS / 4); i += SR_THREADS) {
+        const int tt = i / (COLS / 4), c4 = (i % (COLS / 4)) * 4;
+        if (col0 + c4 < p.vdim) sr_cp16(vb + tt * COLS + c4, p.v + (row0 + tt) * p.v_ld + (size_t)h * p.vdim + col0 + c4);
+      }
+    } else {
+      for (int i = tid; i < nt * p.dim; i += SR_THREADS) {
+        const int tt = i / p.dim, r = i % p.dim, dst = tt * ROW + r + 4 * (r / RPL);
+        sr_cp4(qb + dst, p.q + (row0 + tt) * p.q_ld + (size_t)grp * p.dim + r);
+        sr_cp4(kb + dst, p.k + (row0 + tt) * p.k_ld + (size_t)grp * p.dim + r);
+      }
+      for (int i = tid; i < nt * COLS; i += SR_THREADS) {
+        const int tt = i / COLS, c = i % COLS;
+        if (col0 + c < p.vdim) sr_cp4(vb + tt * COLS + c, p.v + (row0 + tt) * p.v_ld + (size_t)h * p.vdim + col0 + c);
+      }
     }
     if (tid < nt) {
-      const size_t row = (size_t)(first + t0 + tid);
-      const float sp = softplus_f(p.a[row * p.a_ld + h] + dtb);
-      g_s[tid] = expf(-A * sp);
-      w_s[tid] = DELTA ? 1.f / (1.f + expf(-p.b[row * p.b_ld + h])) : sp;
+      sr_cp4(a_s + buf * T + tid, p.a + (row0 + tid) * p.a_ld + h);
+      if (DELTA) sr_cp4(b_s + buf * T + tid, p.b + (row0 + tid) * p.b_ld + h);
     }
-    __syncthreads();
+  };
+
+  const int chunks = (n + T - 1) / T;
+  __syncthreads();                                 // the tile is read; the zeros are in place
+  if (chunks > 0) fetch(0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int c = 0; c < chunks; ++c) {
+    const int buf = c & 1, t0 = c * T, nt = min(T, n - t0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                               // chunk c has landed for all; chunk c - 1 is through, its read-outs are added
+    if (c + 1 < chunks) fetch(c + 1);              // into the buffer chunk c - 1 has left
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    float* qb = q_s + buf * T * ROW;
+    float* kb = k_s + buf * T * ROW;
+    const float* vb = v_s + buf * T * COLS;
+    if (tid < nt) {
+      const float sp = softplus_f(a_s[buf * T + tid] + dtb);
+      g_s[tid] = expf(-A * sp);
+      w_s[tid] = DELTA ? 1.f / (1.f + expf(-b_s[buf * T + tid])) : sp;
+    }
     if (p.unit_norm) {
-      for (int tt = warp; tt < nt; tt += (SR_COLS * SR_SUB) / 32) {
+      for (int tt = warp; tt < nt; tt += SR_THREADS / 32) {
+        float* qr = qb + tt * ROW;
+        float* kr = kb + tt * ROW;
         float sq = 0.f, sk = 0.f;
-        for (int r = lane; r < p.dim; r += 32) { sq += q_s[tt][r] * q_s[tt][r]; sk += k_s[tt][r] * k_s[tt][r]; }
+        for (int r = lane; r < p.dim; r += 32) { const int at = r + 4 * (r / RPL); sq += qr[at] * qr[at]; sk += kr[at] * kr[at]; }
         sq = warp_sum(sq); sk = warp_sum(sk);
         const float fq = p.q_scale / sqrtf(sq + p.unit_eps), fk = 1.f / sqrtf(sk + p.unit_eps);
-        for (int r = lane; r < p.dim; r += 32) { q_s[tt][r] *= fq; k_s[tt][r] *= fk; }
+        for (int r = lane; r < p.dim; r += 32) { const int at = r + 4 * (r / RPL); qr[at] *= fq; kr[at] *= fk; }
       }
-      __syncthreads();
     }
+    __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float g = g_s[tt], w = w_s[tt], vj = v_s[tt][col_local];
-      const float* kk = k_s[tt];
-      const float* qq = q_s[tt];
+      const float g = g_s[tt], w = w_s[tt], vj = vb[tt * COLS + col_local];
+      float kk[RPL], qq[RPL];
+#pragma unroll
+      for (int i = 0; i < RPL; i += 4) {
+        *reinterpret_cast<float4*>(kk + i) = *reinterpret_cast<const float4*>(kb + tt * ROW + sub * (RPL + 4) + i);
+        *reinterpret_cast<float4*>(qq + i) = *reinterpret_cast<const float4*>(qb + tt * ROW + sub * (RPL + 4) + i);
+      }
       float u;
       if (DELTA) {
-        float d0 = 0.f, d1 = 0.f;
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < RPL; i += 2) {
-          d0 = fmaf(s[i], kk[sub + SR_SUB * i], d0);
-          d1 = fmaf(s[i + 1], kk[sub + SR_SUB * (i + 1)], d1);
+        for (int i = 0; i < RPL; i += 4) {
+          d0 = fmaf(s[i], kk[i], d0); d1 = fmaf(s[i + 1], kk[i + 1], d1);
+          d2 = fmaf(s[i + 2], kk[i + 2], d2); d3 = fmaf(s[i + 3], kk[i + 3], d3);
         }
-        float d = d0 + d1;
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        float d = (d0 + d1) + (d2 + d3);
+#pragma unroll
+        for (int m = 1; m < SUB; m <<= 1) d += __shfl_xor_sync(0xffffffffu, d, m);
         u = w * (vj - g * d);
       } else {
         u = w * vj;
       }
-      float o0 = 0.f, o1 = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < RPL; i += 2) {
-        s[i] = fmaf(g, s[i], kk[sub + SR_SUB * i] * u);
-        s[i + 1] = fmaf(g, s[i + 1], kk[sub + SR_SUB * (i + 1)] * u);
-        o0 = fmaf(s[i], qq[sub + SR_SUB * i], o0);
-        o1 = fmaf(s[i + 1], qq[sub + SR_SUB * (i + 1)], o1);
+      for (int i = 0; i < RPL; i += 4) {
+        s[i] = fmaf(g, s[i], kk[i] * u); s[i + 1] = fmaf(g, s[i + 1], kk[i + 1] * u);
+        s[i + 2] = fmaf(g, s[i + 2], kk[i + 2] * u); s[i + 3] = fmaf(g, s[i + 3], kk[i + 3] * u);
+        o0 = fmaf(s[i], qq[i], o0); o1 = fmaf(s[i + 1], qq[i + 1], o1);
+        o2 = fmaf(s[i + 2], qq[i + 2], o2); o3 = fmaf(s[i + 3], qq[i + 3], o3);
       }
-      float o = o0 + o1;
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (sub == 0 && col_ok) p.out[(size_t)(first + t0 + tt) * p.out_ld + (size_t)h * p.vdim + col] = o + Dh * vj;
+      o_s[tt * SR_THREADS + tid] = (o0 + o1) + (o2 + o3);          // [tt][col_local][sub]
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * COLS; i += SR_THREADS) {
+      const int tt = i / COLS, cc = i % COLS, col = col0 + cc;
+      const float* part = o_s + tt * SR_THREADS + cc * SUB;
+      float o = (part[0] + part[1]) + (part[2] + part[3]);
+      if (SUB == 8) o += (part[4] + part[5]) + (part[6] + part[7]);
+      if (col < p.vdim) p.out[(size_t)(first + t0 + tt) * p.out_ld + (size_t)h * p.vdim + col] = o + Dh * vb[tt * COLS + cc];
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                                 // the last read-outs are added: the tile is free for the state
 #pragma unroll
-  for (int i = 0; i < RPL; ++i) {
-    const int r = sub + SR_SUB * i;
-    if (col_ok && r < p.dim) S[(size_t)r * p.vdim + col] = s[i];
+  for (int i = 0; i < RPL; ++i) o_s[(sub * RPL + i) * COLS + (col_local + shift) % COLS] = s[i];
+  __syncthreads();
+  for (int i = tid; i < DP * COLS; i += SR_THREADS) {
+    const int r = i / COLS, c = i % COLS, col = col0 + c;
+    if (r < p.dim && col < p.vdim) S[(size_t)r * p.vdim + col] = o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS];
   }
 }
 
@@ -191,16 +267,25 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
   p.A_log = A_log; p.dt_bias = dt_bias; p.D = D; p.state = state; p.out = out; p.out_ld = out_ld;
   p.cu_tokens = cu_tokens; p.slots = slots; p.heads = heads; p.groups = groups; p.dim = dim; p.vdim = vdim;
   p.unit_norm = unit_norm; p.q_scale = q_scale; p.unit_eps = unit_eps;
-  dim3 grid((vdim + lb::SR_COLS - 1) / lb::SR_COLS, heads, num_seqs), block(lb::SR_COLS * lb::SR_SUB);
-#define LB_SR(RPL)                                                                                        \
-  do {                                                                                                    \
-    if (delta) lb::launch(lb::state_recurrence_kernel<true, RPL>, grid, block, 0, stream, p);             \
-    else lb::launch(lb::state_recurrence_kernel<false, RPL>, grid, block, 0, stream, p);                  \
+  auto aligned = [](const float* x, long long ld) { return ((uintptr_t)x % 16 == 0) && ld % 4 == 0; };
+  p.vec = dim % 4 == 0 && vdim % 4 == 0 && aligned(q, q_ld) && aligned(k, k_ld) && aligned(v, v_ld);
+#define LB_SR(RPL, SUB)                                                                                             \
+  do {                                                                                                              \
+    const size_t smem = (size_t)lb::sr_smem_floats(RPL, SUB) * sizeof(float);                                       \
+    static bool cfg = false;                                                                                        \
+    if (!cfg) {                                                                                                     \
+      cudaFuncSetAttribute(lb::state_recurrence_kernel<true, RPL, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+      cudaFuncSetAttribute(lb::state_recurrence_kernel<false, RPL, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      cfg = true;                                                                                                   \
+    }                                                                                                               \
+    dim3 grid((vdim + lb::SR_THREADS / SUB - 1) / (lb::SR_THREADS / SUB), heads, num_seqs), block(lb::SR_THREADS); \
+    if (delta) lb::launch(lb::state_recurrence_kernel<true, RPL, SUB>, grid, block, smem, stream, p);               \
+    else lb::launch(lb::state_recurrence_kernel<false, RPL, SUB>, grid, block, smem, stream, p);                    \
   } while (0)
-  if (dim <= 32) LB_SR(8);
-  else if (dim <= 64) LB_SR(16);
-  else if (dim <= 128) LB_SR(32);
-  else LB_SR(64);
+  if (dim <= 32) LB_SR(8, 4);
+  else if (dim <= 64) LB_SR(16, 4);
+  else if (dim <= 128) LB_SR(16, 8);
+  else LB_SR(32, 8);
 #undef LB_SR
   LB_CHECK_LAUNCH("state_recurrence");
   return 0;
