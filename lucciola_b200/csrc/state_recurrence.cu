@@ -27,7 +27,7 @@
 
 namespace lb {
 
-constexpr int SR_TOKENS = 16;    // tokens staged at a time
+constexpr int SR_TOKENS = 16;    // tokens staged at a time; 1 in steps of single tokens, whose CTAs then need a fifth of the shared memory
 constexpr int SR_THREADS = 128;
 
 struct StateRecurrenceParams {
@@ -39,6 +39,7 @@ struct StateRecurrenceParams {
   int heads, groups, dim, vdim, unit_norm;
   float q_scale, unit_eps;
   int vec;                       // q, k, v rows start on 16-byte boundaries and hold whole 16-byte pieces
+  int svec;                      // so do the state's rows
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
@@ -52,24 +53,25 @@ __device__ __forceinline__ void sr_cp16(float* dst, const float* src) {
 
 // floats of shared memory: q and k (two buffers of 16 rows of (RPL + 4) * SUB), v, a, b (two buffers), g, w, and the
 // tile that holds the lanes' partial read-outs of a chunk or, at both ends, the CTA's part of the state
-__host__ __device__ constexpr int sr_smem_floats(int rpl, int sub) {
+__host__ __device__ constexpr int sr_smem_floats(int rpl, int sub, int tokens) {
   const int cols = SR_THREADS / sub, row = (rpl + 4) * sub;
-  const int tile = SR_TOKENS * SR_THREADS > rpl * sub * cols ? SR_TOKENS * SR_THREADS : rpl * sub * cols;
-  return 4 * SR_TOKENS * row + 2 * SR_TOKENS * cols + 4 * SR_TOKENS + 2 * SR_TOKENS + tile;
+  const int tile = tokens * SR_THREADS > rpl * sub * cols ? tokens * SR_THREADS : rpl * sub * cols;
+  return 4 * tokens * row + 2 * tokens * cols + 6 * (tokens < 4 ? 4 : tokens) + tile;
 }
 
-template <bool DELTA, int RPL, int SUB>
+template <bool DELTA, int RPL, int SUB, int TOK>
 __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecurrenceParams p) {
-  constexpr int T = SR_TOKENS, COLS = SR_THREADS / SUB, ROW = (RPL + 4) * SUB, DP = RPL * SUB;
+  constexpr int T = TOK, COLS = SR_THREADS / SUB, ROW = (RPL + 4) * SUB, DP = RPL * SUB;
   extern __shared__ __align__(16) float sr_smem[];
   float* q_s = sr_smem;                           // [2][T][ROW]: row r of a token at r + 4 * (r / RPL)
   float* k_s = q_s + 2 * T * ROW;
   float* v_s = k_s + 2 * T * ROW;                 // [2][T][COLS]
-  float* a_s = v_s + 2 * T * COLS;                // [2][T] as the product left them
-  float* b_s = a_s + 2 * T;
-  float* g_s = b_s + 2 * T;                       // [T] decay
-  float* w_s = g_s + T;                           // [T] write strength
-  float* o_s = w_s + T;                           // [T][COLS][SUB] partial read-outs; the state's tile [DP][COLS] at both ends
+  constexpr int TS = T < 4 ? 4 : T;               // the small arrays in whole 16-byte words, so that the tile behind them is aligned
+  float* a_s = v_s + 2 * T * COLS;                // [2][TS] as the product left them
+  float* b_s = a_s + 2 * TS;
+  float* g_s = b_s + 2 * TS;                      // [TS] decay
+  float* w_s = g_s + TS;                          // [TS] write strength
+  float* o_s = w_s + TS;                          // [T][COLS][SUB] partial read-outs; the state's tile [DP][COLS] at both ends
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = tid % SUB, col_local = tid / SUB;
@@ -78,16 +80,25 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
   const int grp = h / (p.heads / p.groups);
   const float A = expf(p.A_log[h]), dtb = p.dt_bias[h];
   const float Dh = p.D ? p.D[h] : 0.f;
-  for (int i = tid; i < 4 * T * ROW + 2 * T * COLS; i += SR_THREADS) sr_smem[i] = 0.f;     // padding and rows past dim stay zero
+  if (p.dim < DP || col0 + COLS > p.vdim)          // rows past dim and columns past vdim stay zero; nothing else of the buffers is read unwritten
+    for (int i = tid; i < 4 * T * ROW + 2 * T * COLS; i += SR_THREADS) sr_smem[i] = 0.f;
   pdl_wait();
   const int first = p.cu_tokens[seq], n = p.cu_tokens[seq + 1] - first;
   float* S = p.state + ((size_t)p.slots[seq] * p.heads + h) * p.dim * p.vdim;
   const int shift = ((32 / SUB) * sub) % COLS;     // a lane's column of the state's tile, turned so that a warp's lanes spread over the banks
 
   // the state: whole lines into the tile, then each lane's rows into registers
-  for (int i = tid; i < DP * COLS; i += SR_THREADS) {
-    const int r = i / COLS, c = i % COLS, col = col0 + c;
-    o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS] = (r < p.dim && col < p.vdim) ? S[(size_t)r * p.vdim + col] : 0.f;
+  if (p.svec) {                                    // 16-byte words: the turn is a multiple of four columns
+    for (int i = tid; i < DP * (COLS / 4); i += SR_THREADS) {
+      const int r = i / (COLS / 4), c = (i % (COLS / 4)) * 4, col = col0 + c;
+      const float4 x = (r < p.dim && col < p.vdim) ? *reinterpret_cast<const float4*>(S + (size_t)r * p.vdim + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(o_s + r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS) = x;
+    }
+  } else {
+    for (int i = tid; i < DP * COLS; i += SR_THREADS) {
+      const int r = i / COLS, c = i % COLS, col = col0 + c;
+      o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS] = (r < p.dim && col < p.vdim) ? S[(size_t)r * p.vdim + col] : 0.f;
+    }
   }
   __syncthreads();
   float s[RPL];
@@ -123,8 +134,8 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
       }
     }
     if (tid < nt) {
-      sr_cp4(a_s + buf * T + tid, p.a + (row0 + tid) * p.a_ld + h);
-      if (DELTA) sr_cp4(b_s + buf * T + tid, p.b + (row0 + tid) * p.b_ld + h);
+      sr_cp4(a_s + buf * TS + tid, p.a + (row0 + tid) * p.a_ld + h);
+      if (DELTA) sr_cp4(b_s + buf * TS + tid, p.b + (row0 + tid) * p.b_ld + h);
     }
   };
 
@@ -142,9 +153,9 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
     float* kb = k_s + buf * T * ROW;
     const float* vb = v_s + buf * T * COLS;
     if (tid < nt) {
-      const float sp = softplus_f(a_s[buf * T + tid] + dtb);
+      const float sp = softplus_f(a_s[buf * TS + tid] + dtb);
       g_s[tid] = expf(-A * sp);
-      w_s[tid] = DELTA ? 1.f / (1.f + expf(-b_s[buf * T + tid])) : sp;
+      w_s[tid] = DELTA ? 1.f / (1.f + expf(-b_s[buf * TS + tid])) : sp;
     }
     if (p.unit_norm) {
       for (int tt = warp; tt < nt; tt += SR_THREADS / 32) {
@@ -205,9 +216,17 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
 #pragma unroll
   for (int i = 0; i < RPL; ++i) o_s[(sub * RPL + i) * COLS + (col_local + shift) % COLS] = s[i];
   __syncthreads();
-  for (int i = tid; i < DP * COLS; i += SR_THREADS) {
-    const int r = i / COLS, c = i % COLS, col = col0 + c;
-    if (r < p.dim && col < p.vdim) S[(size_t)r * p.vdim + col] = o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS];
+  if (p.svec) {
+    for (int i = tid; i < DP * (COLS / 4); i += SR_THREADS) {
+      const int r = i / (COLS / 4), c = (i % (COLS / 4)) * 4, col = col0 + c;
+      if (r < p.dim && col < p.vdim)
+        *reinterpret_cast<float4*>(S + (size_t)r * p.vdim + col) = *reinterpret_cast<const float4*>(o_s + r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS);
+    }
+  } else {
+    for (int i = tid; i < DP * COLS; i += SR_THREADS) {
+      const int r = i / COLS, c = i % COLS, col = col0 + c;
+      if (r < p.dim && col < p.vdim) S[(size_t)r * p.vdim + col] = o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS];
+    }
   }
 }
 
@@ -215,37 +234,40 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
 //   gate_first = 0:  out = y / rms_group(y) * w * act(gate)           (the gated delta rule: a group is a head)
 //   gate_first = 1:  z = y * act(gate);  out = z / rms_group(z) * w     (Mamba-2: the gate comes before the norm)
 // w has `wn` entries and is read at column % wn (wn = the group's size: one weight shared by the groups).
-// act: 0 silu, 1 sigmoid.  A warp a group, the groups of a row in turn.
+// act: 0 silu, 1 sigmoid.  A CTA a (row, group): its warps' sums of squares are added in warp order.
 template <typename TO>
 __global__ void gated_group_norm_kernel(TO* __restrict__ out, long long out_ld, const float* __restrict__ y, long long y_ld,
                                         const float* __restrict__ gate, long long gate_ld, const float* __restrict__ w, int wn,
                                         int n, int groups, int gate_first, int act, float eps, float scale) {
+  __shared__ float part[8];
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int t = blockIdx.x, g = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int gs = n / groups;
-  const float* yr = y + (size_t)t * y_ld;
-  const float* gr = gate + (size_t)t * gate_ld;
-  for (int g = warp; g < groups; g += nwarps) {
-    float ss = 0.f;
-    for (int c = lane; c < gs; c += 32) {
-      float x = yr[g * gs + c];
-      if (gate_first) {
-        const float z = gr[g * gs + c];
-        x *= act == 0 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));
-      }
-      ss += x * x;
+  const float* yr = y + (size_t)t * y_ld + (size_t)g * gs;
+  const float* gr = gate + (size_t)t * gate_ld + (size_t)g * gs;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    float x = yr[c];
+    if (gate_first) {
+      const float z = gr[c];
+      x *= act == 0 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));
     }
-    ss = warp_sum(ss);
-    const float inv = 1.f / sqrtf(ss / (float)gs + eps);
-    for (int c = lane; c < gs; c += 32) {
-      const int col = g * gs + c;
-      const float z = gr[col];
-      const float a = act == 0 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));
-      const float x = yr[col];
-      const float r = gate_first ? (x * a) * inv * w[col % wn] : x * inv * w[col % wn] * a;
-      out[(size_t)t * out_ld + col] = from_f32<TO>(r * scale);
-    }
+    ss += x * x;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) part[warp] = ss;
+  __syncthreads();
+  ss = 0.f;
+  for (int i = 0; i < nwarps; ++i) ss += part[i];
+  const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    const int col = g * gs + c;
+    const float z = gr[c];
+    const float a = act == 0 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));
+    const float x = yr[c];
+    const float r = gate_first ? (x * a) * inv * w[col % wn] : x * inv * w[col % wn] * a;
+    out[(size_t)t * out_ld + col] = from_f32<TO>(r * scale);
   }
 }
 
@@ -255,7 +277,7 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
                                   long long v_ld, const float* a, long long a_ld, const float* b, long long b_ld,
                                   const float* A_log, const float* dt_bias, const float* D, float* state, float* out,
                                   long long out_ld, const int* cu_tokens, const int* slots, int num_seqs, int heads, int groups,
-                                  int dim, int vdim, int unit_norm, float q_scale, float unit_eps, cudaStream_t stream) {
+                                  int dim, int vdim, int unit_norm, float q_scale, float unit_eps, int single_tokens, cudaStream_t stream) {
   LB_CHECK_ARG(q && k && v && a && A_log && dt_bias && state && out && cu_tokens && slots && (!delta || b),
                "state_recurrence: null argument");
   LB_CHECK_ARG(heads > 0 && groups > 0 && heads % groups == 0, "state_recurrence: %d heads are not a multiple of %d groups", heads, groups);
@@ -269,23 +291,31 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
   p.unit_norm = unit_norm; p.q_scale = q_scale; p.unit_eps = unit_eps;
   auto aligned = [](const float* x, long long ld) { return ((uintptr_t)x % 16 == 0) && ld % 4 == 0; };
   p.vec = dim % 4 == 0 && vdim % 4 == 0 && aligned(q, q_ld) && aligned(k, k_ld) && aligned(v, v_ld);
-#define LB_SR(RPL, SUB)                                                                                             \
+  p.svec = vdim % 4 == 0 && (uintptr_t)state % 16 == 0;
+#define LB_SR1(RPL, SUB, TOK)                                                                                       \
   do {                                                                                                              \
-    const size_t smem = (size_t)lb::sr_smem_floats(RPL, SUB) * sizeof(float);                                       \
+    const size_t smem = (size_t)lb::sr_smem_floats(RPL, SUB, TOK) * sizeof(float);                                  \
     static bool cfg = false;                                                                                        \
     if (!cfg) {                                                                                                     \
-      cudaFuncSetAttribute(lb::state_recurrence_kernel<true, RPL, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-      cudaFuncSetAttribute(lb::state_recurrence_kernel<false, RPL, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      cudaFuncSetAttribute(lb::state_recurrence_kernel<true, RPL, SUB, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+      cudaFuncSetAttribute(lb::state_recurrence_kernel<false, RPL, SUB, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       cfg = true;                                                                                                   \
     }                                                                                                               \
     dim3 grid((vdim + lb::SR_THREADS / SUB - 1) / (lb::SR_THREADS / SUB), heads, num_seqs), block(lb::SR_THREADS); \
-    if (delta) lb::launch(lb::state_recurrence_kernel<true, RPL, SUB>, grid, block, smem, stream, p);               \
-    else lb::launch(lb::state_recurrence_kernel<false, RPL, SUB>, grid, block, smem, stream, p);                    \
+    if (delta) lb::launch(lb::state_recurrence_kernel<true, RPL, SUB, TOK>, grid, block, smem, stream, p);          \
+    else lb::launch(lb::state_recurrence_kernel<false, RPL, SUB, TOK>, grid, block, smem, stream, p);               \
+  } while (0)
+  // a step of single tokens stages one token at a time: the same sums in the same order, a fifth of the shared memory
+#define LB_SR(RPL, SUB)                                                                                             \
+  do {                                                                                                              \
+    if (single_tokens) LB_SR1(RPL, SUB, 1);                                                                         \
+    else LB_SR1(RPL, SUB, lb::SR_TOKENS);                                                                           \
   } while (0)
   if (dim <= 32) LB_SR(8, 4);
   else if (dim <= 64) LB_SR(16, 4);
   else if (dim <= 128) LB_SR(16, 8);
   else LB_SR(32, 8);
+#undef LB_SR1
 #undef LB_SR
   LB_CHECK_LAUNCH("state_recurrence");
   return 0;
@@ -298,9 +328,11 @@ LB_EXPORT int lb_gated_group_norm(void* out, int out_dtype, long long out_ld, co
   LB_CHECK_ARG(out && y && gate && w && num_rows >= 0 && n > 0 && groups > 0 && n % groups == 0 && wn > 0 && (act == 0 || act == 1),
                "gated_group_norm: bad arguments rows=%d n=%d groups=%d", num_rows, n, groups);
   if (num_rows == 0) return 0;
-  int warps = groups < 8 ? groups : 8;
+  LB_CHECK_ARG(groups <= 65535, "gated_group_norm: %d groups", groups);
+  const int gs = n / groups;
+  const int warps = gs >= 1024 ? 8 : gs >= 256 ? 4 : gs >= 64 ? 2 : 1;      // by the group's size alone
   LB_DISPATCH_DTYPE(out_dtype, TO, {
-    lb::launch(lb::gated_group_norm_kernel<TO>, dim3(num_rows), dim3(warps * 32), 0, stream, (TO*)out, out_ld, y, y_ld, gate, gate_ld,
+    lb::launch(lb::gated_group_norm_kernel<TO>, dim3(num_rows, groups), dim3(warps * 32), 0, stream, (TO*)out, out_ld, y, y_ld, gate, gate_ld,
                w, wn, n, groups, gate_first, act, eps, scale);
   })
   LB_CHECK_LAUNCH("gated_group_norm");

@@ -75,7 +75,7 @@ _SIGNATURES = {
     "lb_short_conv_state": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lb_state_recurrence": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                             c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
-                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "lb_gated_group_norm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "lb_bias_rmsnorm_cols": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
@@ -401,7 +401,7 @@ def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch
     _call("lb_state_recurrence", 1 if delta else 0, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
           a.data_ptr(), a.stride(0), _ptr(b), b.stride(0) if b is not None else 0, A_log.data_ptr(), dt_bias.data_ptr(), _ptr(D),
           state.data_ptr(), out.data_ptr(), out.stride(0), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs,
-          heads, groups, dim, vdim, 1 if unit_norm else 0, q_scale, unit_eps, stream)
+          heads, groups, dim, vdim, 1 if unit_norm else 0, q_scale, unit_eps, 1 if T == step.num_seqs else 0, stream)
 
 
 def gated_group_norm(out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
