@@ -234,16 +234,18 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
 //   gate_first = 0:  out = y / rms_group(y) * w * act(gate)           (the gated delta rule: a group is a head)
 //   gate_first = 1:  z = y * act(gate);  out = z / rms_group(z) * w     (Mamba-2: the gate comes before the norm)
 // w has `wn` entries and is read at column % wn (wn = the group's size: one weight shared by the groups).
-// act: 0 silu, 1 sigmoid.  A CTA a (row, group): its warps' sums of squares are added in warp order.
+// act: 0 silu, 1 sigmoid.  One to eight warps a (row, group), by the group's size, and as many groups of a row in a CTA
+// (threadIdx.y) as make it 256 threads; a group's warps add their sums of squares in warp order.
 template <typename TO>
 __global__ void gated_group_norm_kernel(TO* __restrict__ out, long long out_ld, const float* __restrict__ y, long long y_ld,
                                         const float* __restrict__ gate, long long gate_ld, const float* __restrict__ w, int wn,
                                         int n, int groups, int gate_first, int act, float eps, float scale) {
-  __shared__ float part[8];
+  __shared__ float part[8][8];
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x, g = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int gs = n / groups;
+  const int t = blockIdx.x, gy = threadIdx.y, g = blockIdx.y * blockDim.y + gy;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gs = g < groups ? n / groups : 0;      // a group past the last has no columns, but meets the others at the barrier
   const float* yr = y + (size_t)t * y_ld + (size_t)g * gs;
   const float* gr = gate + (size_t)t * gate_ld + (size_t)g * gs;
   float ss = 0.f;
@@ -256,11 +258,11 @@ __global__ void gated_group_norm_kernel(TO* __restrict__ out, long long out_ld, 
     ss += x * x;
   }
   ss = warp_sum(ss);
-  if (lane == 0) part[warp] = ss;
+  if (lane == 0) part[gy][warp] = ss;
   __syncthreads();
   ss = 0.f;
-  for (int i = 0; i < nwarps; ++i) ss += part[i];
-  const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+  for (int i = 0; i < nwarps; ++i) ss += part[gy][i];
+  const float inv = 1.f / sqrtf(ss / (float)(n / groups) + eps);
   for (int c = threadIdx.x; c < gs; c += blockDim.x) {
     const int col = g * gs + c;
     const float z = gr[c];
@@ -330,10 +332,13 @@ LB_EXPORT int lb_gated_group_norm(void* out, int out_dtype, long long out_ld, co
   if (num_rows == 0) return 0;
   LB_CHECK_ARG(groups <= 65535, "gated_group_norm: %d groups", groups);
   const int gs = n / groups;
-  const int warps = gs >= 1024 ? 8 : gs >= 256 ? 4 : gs >= 64 ? 2 : 1;      // by the group's size alone
+  const int warps = gs >= 1024 ? 8 : gs >= 512 ? 4 : gs >= 256 ? 2 : 1;     // by the group's size alone
+  int per_cta = 8 / warps;                                                  // groups of a row in one CTA
+  if (per_cta > groups) per_cta = groups;
+  LB_CHECK_ARG((groups + per_cta - 1) / per_cta <= 65535, "gated_group_norm: %d groups", groups);
   LB_DISPATCH_DTYPE(out_dtype, TO, {
-    lb::launch(lb::gated_group_norm_kernel<TO>, dim3(num_rows, groups), dim3(warps * 32), 0, stream, (TO*)out, out_ld, y, y_ld, gate, gate_ld,
-               w, wn, n, groups, gate_first, act, eps, scale);
+    lb::launch(lb::gated_group_norm_kernel<TO>, dim3(num_rows, (groups + per_cta - 1) / per_cta), dim3(warps * 32, per_cta), 0, stream,
+               (TO*)out, out_ld, y, y_ld, gate, gate_ld, w, wn, n, groups, gate_first, act, eps, scale);
   })
   LB_CHECK_LAUNCH("gated_group_norm");
   return 0;

@@ -62,7 +62,7 @@ def in_portions(forward, xs, slots, schedule):
     return [torch.cat(g) for g in got]
 
 
-SCHEDULE = ([1, 2], [17, 1], [3, 1], [16, 1], [2, 0], [40, 0])
+SCHEDULE = ([1, 2], [1, 1], [17, 1], [3, 1], [16, 1], [2, 0], [1, 0], [40, 0])      # [1, 1], [1, 0]: steps of single tokens
 
 
 # ---- each mechanism alone --------------------------------------------------------------------------------------------
