@@ -86,7 +86,7 @@ __global__ void plain_attention_kernel(PlainAttnParams p) {
         }
       }
       const float m_new = fmaxf(m, warp_max(s));
-      if (m_new == -INFINITY) continue;          // no key of this round has a page: uniform over the warp
+      if (m_new == -INFINITY) continue;          // no key of this pass has a page: uniform over the warp
       const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
       const float pj = (off >= 0) ? expf(s - m_new) : 0.f;
       l = l * alpha + warp_sum(pj);
