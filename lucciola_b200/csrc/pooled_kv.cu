@@ -61,11 +61,16 @@ __global__ void pool_kv_kernel(const T* __restrict__ k_cache, const T* __restric
     const int e = is_k ? i : i - d, width = is_k ? d : dv;
     const T* src = is_k ? k_cache : v_cache;
     float sum = 0.f;
-    for (int j = 0; j < P; ++j) {
-      const int pos = b * P + j;
-      const int page = bt[pos / page_size];
-      if (page < 0) continue;
-      sum += to_f32(src[(((size_t)page * num_kv_heads + kvh) * page_size + pos % page_size) * width + e]);
+    for (int j0 = 0; j0 < P; j0 += 8) {          // eight loads in flight, then their sum in token order
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int pos = b * P + j0 + u;
+        const int page = j0 + u < P ? bt[pos / page_size] : -1;
+        x[u] = page >= 0 ? to_f32(src[(((size_t)page * num_kv_heads + kvh) * page_size + pos % page_size) * width + e]) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) sum += x[u];
     }
     (is_k ? pool_k : pool_v)[dest_off * width + e] = from_f32<T>(sum / (float)P);
   }
