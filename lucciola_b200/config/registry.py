@@ -51,4 +51,4 @@ def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
 
 def _ensure_builtin() -> None:
     # The built-in models register themselves on import.
-    from ..models import bonolorn, nelovik, qwen3, riruzen  # noqa: F401
+    from ..models import bonolorn, nelovik, qwen3, riruzen, venitar  # noqa: F401

@@ -58,6 +58,7 @@ struct FlashParams {
   int pool;                                 // P > 0: behind the window a row at position i also sees entry b of a second paged
   const bf16* pool_k; const bf16* pool_v;   // cache (same page size and heads) for every b with (b + 1) P - 1 <= i - window,
   const int* pool_table; int pool_max_pages;// in the same softmax and without a distance bias
+  int chunk;                                // C > 0: a row at position i sees no key before floor(i / C) * C (positions in runs of C)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -238,7 +239,8 @@ flash_attention_kernel(FlashParams p) {
   // Keys this tile can see, and the part of them this split handles (multiples of a stage).  With pooled blocks the
   // tile's keys are laid out along one axis u: first the pooled entries 0 .. nb_tile - 1 that its last row sees, padded to
   // whole stages (PB places), then the keys lo_tile .. pos_last; a stage is all entries or all keys.
-  const int lo_tile = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  int lo_tile = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  if (p.chunk > 0) lo_tile = max(lo_tile, pos0 - pos0 % p.chunk);       // a chunk's start never moves back as positions grow
   const int span = pos_last - lo_tile + 1;
   const int nb_tile = (p.pool > 0 && pos_last - p.window + 1 >= p.pool) ? (pos_last - p.window + 1) / p.pool : 0;
   const int PB = (nb_tile + FA_KEYS - 1) / FA_KEYS * FA_KEYS;
@@ -320,6 +322,7 @@ flash_attention_kernel(FlashParams p) {
     const int r = r0 + 8 * h;
     row_pos[h] = r < rows ? pos0 + r / G : -1;                  // -1: no key passes the mask
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+    if (p.chunk > 0 && row_pos[h] >= 0) row_lo[h] = max(row_lo[h], row_pos[h] - row_pos[h] % p.chunk);
     row_bias[h] = (p.slopes && r < rows) ? p.slopes[kvh * G + r % G] * p.inv_scale : 0.f;
     row_nb[h] = (p.pool > 0 && row_pos[h] - p.window + 1 >= p.pool) ? (row_pos[h] - p.window + 1) / p.pool : 0;
   }
@@ -377,7 +380,7 @@ flash_attention_kernel(FlashParams p) {
     // ---- mask, online softmax ----------------------------------------------------------------
     // Rows past the tile's last (zero queries, positions -1) need no mask of their own: what they gather is never
     // written, and it is finite, because keys and values of slots that hold nothing lie at or past kend.
-    const bool need_mask = pooled || (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend);
+    const bool need_mask = pooled || (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (p.chunk > 0) || (kbase + FA_KEYS > kend);
     const bool biased = p.slopes && !pooled;
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
@@ -950,21 +953,23 @@ LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads
 // softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  sinks (optional, float32 [nq]): the softmax's
 // denominator also holds exp(sinks[h]).  pool = P > 0 (needs a window): a query at position i also sees entry b of the
 // second paged cache pool_k / pool_v (same page size and heads, block table pool_table with pool_max_pages columns) for
-// every b with (b + 1) P - 1 <= i - window.  Any of the three keeps the launch off the TMA kernel.
+// every b with (b + 1) P - 1 <= i - window.  chunk = C > 0: positions in runs of C from the sequence's start, a query sees
+// its own run only.  Any of the four keeps the launch off the TMA kernel.
 LB_EXPORT int lb_attention_flash_ex(const void* q, void* out, const void* k_cache, const void* v_cache,
                                     const int* positions, const int* block_table, const void* tiles, int num_tiles,
                                     int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
                                     int num_pages, int window, float scale, int splits, int part_rows, float* workspace,
                                     long long workspace_elems, int kv_share, const float* slopes, float softcap,
                                     const float* sinks, int pool, const void* pool_k, const void* pool_v, const int* pool_table,
-                                    int pool_max_pages, cudaStream_t stream) {
+                                    int pool_max_pages, int chunk, cudaStream_t stream) {
+  LB_CHECK_ARG(chunk >= 0 && (chunk == 0 || pool == 0), "attention_flash: chunks of %d keys (and no pooled blocks with them)", chunk);
   LB_CHECK_ARG((slopes == nullptr && sinks == nullptr && !(softcap > 0.f)) || scale > 0.f,
                "attention_flash: a distance bias, a cap and a sink need a positive scale");
   LB_CHECK_ARG(softcap >= 0.f, "attention_flash: a cap of %f", (double)softcap);
   LB_CHECK_ARG(pool == 0 || (pool > 0 && window > 0 && pool_k && pool_v && pool_table && pool_max_pages > 0 && kv_share == 1 &&
                              ((uintptr_t)pool_k % 16 == 0) && ((uintptr_t)pool_v % 16 == 0)),
                "attention_flash: pooled blocks need a window, the pooled cache and its block table");
-  if (softcap > 0.f || sinks || pool > 0) num_pages = 0;
+  if (softcap > 0.f || sinks || pool > 0 || chunk > 0) num_pages = 0;
   LB_CHECK_ARG(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
                "attention_flash: %d query heads are not a multiple of %d kv heads", num_q_heads, num_kv_heads);
   LB_CHECK_ARG(kv_share >= 1 && num_kv_heads % kv_share == 0, "attention_flash: %d kv heads cannot share cached heads %d by %d",
@@ -1004,7 +1009,7 @@ LB_EXPORT int lb_attention_flash_ex(const void* q, void* out, const void* k_cach
   p.slopes = slopes; p.inv_scale = (slopes || sinks) ? 1.f / scale : 0.f;
   p.cap_raw = softcap > 0.f ? softcap / scale : 0.f; p.inv_cap_raw = softcap > 0.f ? scale / softcap : 0.f;
   p.sinks = sinks; p.pool = pool; p.pool_k = (const lb::bf16*)pool_k; p.pool_v = (const lb::bf16*)pool_v;
-  p.pool_table = pool_table; p.pool_max_pages = pool_max_pages;
+  p.pool_table = pool_table; p.pool_max_pages = pool_max_pages; p.chunk = chunk;
   dim3 grid(num_tiles, num_kv_heads, splits);
   const int dp = head_dim <= 64 ? 64 : 128;
   const int smem = part_rows <= 16 ? (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2   // query tile + 3 stages
@@ -1093,5 +1098,5 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
                                  long long workspace_elems, int kv_share, const float* slopes, cudaStream_t stream) {
   return lb_attention_flash_ex(q, out, k_cache, v_cache, positions, block_table, tiles, num_tiles, num_q_heads, num_kv_heads,
                                head_dim, page_size, max_pages, num_pages, window, scale, splits, part_rows, workspace,
-                               workspace_elems, kv_share, slopes, 0.f, nullptr, 0, nullptr, nullptr, nullptr, 0, stream);
+                               workspace_elems, kv_share, slopes, 0.f, nullptr, 0, nullptr, nullptr, nullptr, 0, 0, stream);
 }

@@ -21,6 +21,9 @@
 // blocks behind the window: with pool = P > 0 the query at position i also sees entry b of a second paged cache (one
 // entry for every P tokens, at "position" b of its own block table) for every b with (b + 1) P - 1 <= i - window,
 // in the same softmax; the entries are the means that lb_pool_kv writes.
+//
+// And chunks: with chunk = C > 0 positions are cut into runs of C counted from the sequence's start, and the query at
+// position i sees the keys floor(i / C) * C .. i only (beside a window, whichever starts later).
 #include "common.cuh"
 
 namespace lb {
@@ -36,6 +39,7 @@ struct PlainAttnParams {
   const float* sinks;      // optional [num_q_heads]
   int pool;                // 0: no pooled blocks; P: one pooled entry for every P tokens
   const void* pool_k; const void* pool_v; const int* pool_table; int pool_max_pages;
+  int chunk;               // 0: none; C: the query at position i sees no key before floor(i / C) * C
 };
 
 template <typename T, int DPL>
@@ -57,7 +61,8 @@ __global__ void plain_attention_kernel(PlainAttnParams p) {
 
   const int pos = p.positions[t];
   const int* bt = p.block_table + (size_t)p.token_seq[t] * p.max_pages;
-  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
   const T* kc = (const T*)p.k_cache;
   const T* vc = (const T*)p.v_cache;
 
@@ -153,7 +158,8 @@ LB_EXPORT int lb_attention_plain(int dtype, const void* q, void* out, const void
                                  int num_kv_heads, int head_dim, int page_size, int max_pages,
                                  int window, float scale, int v_dim, const float* slopes, float softcap,
                                  const float* sinks, int pool, const void* pool_k, const void* pool_v, const int* pool_table,
-                                 int pool_max_pages, cudaStream_t stream) {
+                                 int pool_max_pages, int chunk, cudaStream_t stream) {
+  LB_CHECK_ARG(chunk >= 0 && (chunk == 0 || pool == 0), "attention_plain: chunks of %d keys (and no pooled blocks with them)", chunk);
   LB_CHECK_ARG(pool == 0 || (pool > 0 && window > 0 && pool_k && pool_v && pool_table && pool_max_pages > 0),
                "attention_plain: pooled blocks need a window, the pooled cache and its block table");
   LB_CHECK_ARG(softcap >= 0.f, "attention_plain: a cap of %f", (double)softcap);
@@ -173,7 +179,7 @@ LB_EXPORT int lb_attention_plain(int dtype, const void* q, void* out, const void
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
   p.page_size = page_size; p.max_pages = max_pages; p.window = window; p.scale = scale; p.v_dim = v_dim; p.slopes = slopes;
   p.softcap = softcap; p.sinks = sinks; p.pool = pool; p.pool_k = pool_k; p.pool_v = pool_v; p.pool_table = pool_table;
-  p.pool_max_pages = pool_max_pages;
+  p.pool_max_pages = pool_max_pages; p.chunk = chunk;
   LB_DISPATCH_DTYPE(dtype, T, { lb::launch_plain<T>(p, num_tokens, stream); })
   LB_CHECK_LAUNCH("attention_plain");
   return 0;

@@ -2,6 +2,7 @@
 // S [dim, vdim] in 32-bit,
 //
 //   q_t = silu(a_t)   k_t = silu(b_t)   v_t = silu(c_t)        a, b, c: this token's columns of the input projection
+//   (or, with act = 0, q, k, v as the columns hold them: a mixer that rotates q and k first, for one)
 //   S_t = decay_h * S_(t-1) + k_t v_t^T
 //   o_t = S_t^T q_t
 //
@@ -29,6 +30,7 @@ struct DecayRecurrenceParams {
   float* out;                           // [T, heads * vdim]
   const int* cu_tokens; const int* slots;
   int heads, dim, vdim;
+  int act;                              // 1: q, k, v pass silu; 0: they are taken as they come
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
@@ -62,14 +64,19 @@ __global__ void __launch_bounds__(MAX_THREADS) decay_recurrence_kernel(DecayRecu
       float k = 0.f, q = 0.f;                         // rows beyond dim: nothing enters, nothing is read
       if (d < p.dim) {
         const float* row = p.pre + (size_t)(first + c0 + tt) * p.ld + h * p.dim + d;
-        q = silu_f(row[p.q_col]);
-        k = silu_f(row[p.k_col]);
+        q = p.act ? silu_f(row[p.q_col]) : row[p.q_col];
+        k = p.act ? silu_f(row[p.k_col]) : row[p.k_col];
       }
       ks[idx] = k; qs[idx] = q;
     }
     for (int idx = threadIdx.x; idx < cn * 32; idx += blockDim.x) {
       const int tt = idx >> 5, ee = blockIdx.x * 32 + (idx & 31);
-      vs[idx] = ee < p.vdim ? silu_f(p.pre[(size_t)(first + c0 + tt) * p.ld + p.v_col + h * p.vdim + ee]) : 0.f;
+      float v = 0.f;
+      if (ee < p.vdim) {
+        v = p.pre[(size_t)(first + c0 + tt) * p.ld + p.v_col + h * p.vdim + ee];
+        if (p.act) v = silu_f(v);
+      }
+      vs[idx] = v;
     }
     __syncthreads();
     for (int tt = 0; tt < cn; ++tt) {
@@ -199,13 +206,13 @@ __global__ void __launch_bounds__(256) decay_chunk_kernel(DecayChunkParams pc) {
 #pragma unroll
     for (int u = 0; u < PER / 2; ++u) {
       const int tt = u * TSTEP + tq;
-      qs[tt * ldq + td] = raw[u] == -INFINITY ? 0.f : silu_fast(raw[u]);
-      ks[tt * ldq + td] = raw[PER / 2 + u] == -INFINITY ? 0.f : silu_fast(raw[PER / 2 + u]);
+      qs[tt * ldq + td] = raw[u] == -INFINITY ? 0.f : (p.act ? silu_fast(raw[u]) : raw[u]);
+      ks[tt * ldq + td] = raw[PER / 2 + u] == -INFINITY ? 0.f : (p.act ? silu_fast(raw[PER / 2 + u]) : raw[PER / 2 + u]);
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
       const int idx = u * nt + threadIdx.x;
-      if (idx < DC_C * 32) vs[idx] = rawv[u] == -INFINITY ? 0.f : silu_fast(rawv[u]);
+      if (idx < DC_C * 32) vs[idx] = rawv[u] == -INFINITY ? 0.f : (p.act ? silu_fast(rawv[u]) : rawv[u]);
     }
   };
 #pragma unroll
@@ -365,7 +372,7 @@ LB_EXPORT int lb_decay_row_split(int num_seqs, int heads, int dim, int vdim, int
 LB_EXPORT int lb_decay_recurrence(const float* pre, long long ld, int q_col, int k_col, int v_col, const float* decay,
                                   float* state, float* out, const int* cu_tokens, const int* slots, int num_seqs,
                                   int heads, int dim, int vdim, int max_tokens_a_seq, int row_split, long long plane,
-                                  cudaStream_t stream) {
+                                  int act, cudaStream_t stream) {
   LB_CHECK_ARG(pre && decay && state && out && cu_tokens && slots, "decay_recurrence: null argument");
   LB_CHECK_ARG(num_seqs >= 0 && heads > 0 && heads <= 65535 && dim > 0 && dim <= 1024 && vdim > 0 && num_seqs <= 65535,
                "decay_recurrence: bad sizes seqs=%d heads=%d dim=%d vdim=%d (dim at most 1024)", num_seqs, heads, dim, vdim);
@@ -373,6 +380,7 @@ LB_EXPORT int lb_decay_recurrence(const float* pre, long long ld, int q_col, int
   lb::DecayRecurrenceParams p;
   p.pre = pre; p.ld = ld; p.q_col = q_col; p.k_col = k_col; p.v_col = v_col; p.decay = decay;
   p.state = state; p.out = out; p.cu_tokens = cu_tokens; p.slots = slots; p.heads = heads; p.dim = dim; p.vdim = vdim;
+  p.act = act ? 1 : 0;
   const bool few = max_tokens_a_seq > 0 && max_tokens_a_seq <= 4;
   cudaError_t e;
   if (row_split >= 1) {

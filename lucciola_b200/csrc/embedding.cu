@@ -7,6 +7,9 @@
 // With a table of learned position vectors the row pos_table[positions[t], :] is added in 32-bit,
 // unscaled, for models that encode positions at the input instead of inside attention.
 //
+// `scale` multiplies the table's row (in 32-bit, before anything is added); `out2`, if given, receives a second copy
+// of the result, for models that add the embedding's output to the stream again later.
+//
 // With a table of frequencies (sin_freq, 64-bit, [ceil(hidden / 2)]) a sinusoidal position vector is added
 // instead: entry 2i gets sin(p * sin_freq[i]), entry 2i + 1 the cosine of the same angle.  The angle is formed
 // and brought into (-pi, pi] in 64-bit, so that a position in the hundreds of thousands costs no digits; sine and
@@ -18,7 +21,8 @@ namespace lb {
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const int* __restrict__ ids,
                                  const TW* __restrict__ table, int hidden, int vocab,
-                                 const TW* __restrict__ pos_table, const int* __restrict__ positions, int max_positions) {
+                                 const TW* __restrict__ pos_table, const int* __restrict__ positions, int max_positions,
+                                 float scale, float* __restrict__ out2) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -26,6 +30,20 @@ __global__ void embedding_kernel(float* __restrict__ out, const int* __restrict_
   if (id < 0 || id >= vocab) id = 0;
   const TW* row = table + (size_t)id * hidden;
   float* dst = out + (size_t)t * hidden;
+  if (scale != 1.f || out2) {                 // a scaled table row, optionally written twice (one copy stays as it is)
+    float* dst2 = out2 ? out2 + (size_t)t * hidden : nullptr;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = to_f32(row[i]) * scale;
+      if (pos_table) {
+        int p = positions[t];
+        if (p < 0 || p >= max_positions) p = 0;
+        v += to_f32(pos_table[(size_t)p * hidden + i]);
+      }
+      dst[i] = v;
+      if (dst2) dst2[i] = v;
+    }
+    return;
+  }
   if (pos_table) {
     int p = positions[t];
     if (p < 0 || p >= max_positions) p = 0;
@@ -65,7 +83,8 @@ __global__ void embedding_sinusoid_kernel(float* __restrict__ out, const int* __
 // (with positions, without pos_table) asks for sinusoidal position vectors instead.
 LB_EXPORT int lb_embedding(float* out, const int* ids, const void* table, int table_dtype,
                            int num_tokens, int hidden, int vocab, const void* pos_table, const int* positions,
-                           int max_positions, const double* sin_freq, cudaStream_t stream) {
+                           int max_positions, const double* sin_freq, float scale, float* out2, cudaStream_t stream) {
+  LB_CHECK_ARG(sin_freq == nullptr || (scale == 1.f && out2 == nullptr), "embedding: sinusoidal positions take no scale and no second copy");
   LB_CHECK_ARG(sin_freq == nullptr || (pos_table == nullptr && positions != nullptr),
                "embedding: sinusoidal positions need the positions and exclude a table of position vectors");
   LB_CHECK_ARG(sin_freq != nullptr || ((pos_table == nullptr) == (positions == nullptr) && (pos_table == nullptr || max_positions > 0)),
@@ -85,7 +104,7 @@ LB_EXPORT int lb_embedding(float* out, const int* ids, const void* table, int ta
   }
   LB_DISPATCH_DTYPE(table_dtype, TW, {
     lb::launch(lb::embedding_kernel<TW>, dim3(num_tokens), dim3(threads), 0, stream, out, ids, (const TW*)table, hidden, vocab,
-               (const TW*)pos_table, positions, max_positions);
+               (const TW*)pos_table, positions, max_positions, scale, out2);
   })
   LB_CHECK_LAUNCH("embedding");
   return 0;

@@ -29,6 +29,7 @@ struct RopeKvParams {
   int num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages;
   float eps;
   int v_dim;                                 // size of a value head (the value pool and v_out have rows of this size)
+  float rot_scale;                           // sines and cosines are multiplied by this (1: a pure rotation)
 };
 
 // TI: the type of q_in, k_in, v_in (a product's output, which may be 32-bit where the heads are stored in bfloat16)
@@ -93,6 +94,7 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
         const float angle = (float)pos * p.inv_freq[i];
         float s, c;
         sincosf(angle, &s, &c);
+        s *= p.rot_scale; c *= p.rot_scale;
         const float x = buf[i], y = buf[i + half];
         dst[i] = from_f32<T>(x * c - y * s);
         dst[i + half] = from_f32<T>(x * s + y * c);
@@ -122,7 +124,10 @@ __global__ void rope_kv_vec_kernel(RopeKvParams p) {
   float cs[VEC], sn[VEC];
   if (p.inv_freq) {
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) sincosf((float)pos * p.inv_freq[(lane & 15) * VEC + i], &sn[i], &cs[i]);
+    for (int i = 0; i < VEC; ++i) {
+      sincosf((float)pos * p.inv_freq[(lane & 15) * VEC + i], &sn[i], &cs[i]);
+      sn[i] *= p.rot_scale; cs[i] *= p.rot_scale;
+    }
   }
   // The token's page does not depend on the kernel ahead either (positions and block tables are the step's inputs).
   int page = -1;
@@ -196,7 +201,63 @@ __global__ void rope_kv_vec_kernel(RopeKvParams p) {
   }
 }
 
+// Rotation in place of 32-bit rows, for mixers that keep q and k in 32-bit (no cache, no norm): up to two column
+// ranges of x [T, ld], each `heads` heads of `head_dim`, whose first rot_dim entries are rotated as above and whose
+// every entry is then multiplied by the range's `scale`.  One warp a head.
+struct RotateRowsParams {
+  float* x; long long ld;
+  const int* positions; const float* inv_freq;
+  int head_dim, rot_dim;
+  float rot_scale;
+  int col[2], heads[2];
+  float scale[2];
+};
+
+__global__ void rotate_rows_kernel(RotateRowsParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int half = p.rot_dim >> 1, d = p.head_dim;
+  const int pos = p.positions[t];
+  const int total = p.heads[0] + p.heads[1];
+  for (int h = blockIdx.y * nwarps + warp; h < total; h += gridDim.y * nwarps) {
+    const int r = h < p.heads[0] ? 0 : 1;
+    float* row = p.x + (size_t)t * p.ld + p.col[r] + (size_t)(r == 0 ? h : h - p.heads[0]) * d;
+    const float sc = p.scale[r];
+    for (int i = lane; i < half; i += 32) {
+      float s, c;
+      sincosf((float)pos * p.inv_freq[i], &s, &c);
+      s *= p.rot_scale; c *= p.rot_scale;
+      const float x = row[i], y = row[i + half];
+      row[i] = (x * c - y * s) * sc;
+      row[i + half] = (x * s + y * c) * sc;
+    }
+    if (sc != 1.f)
+      for (int i = p.rot_dim + lane; i < d; i += 32) row[i] *= sc;
+  }
+}
+
 }  // namespace lb
+
+LB_EXPORT int lb_rotate_rows(float* x, long long ld, int num_tokens, const int* positions, const float* inv_freq, int head_dim,
+                             int rot_dim, float rot_scale, int col0, int heads0, float scale0, int col1, int heads1, float scale1,
+                             cudaStream_t stream) {
+  LB_CHECK_ARG(x && positions && head_dim > 0 && rot_dim >= 0 && rot_dim <= head_dim && rot_dim % 2 == 0 && (rot_dim == 0 || inv_freq),
+               "rotate_rows: rotary size %d must be even and at most head_dim %d", rot_dim, head_dim);
+  LB_CHECK_ARG(heads0 >= 0 && heads1 >= 0 && col0 >= 0 && col1 >= 0 && num_tokens >= 0, "rotate_rows: bad ranges");
+  if (num_tokens == 0 || heads0 + heads1 == 0) return 0;
+  lb::RotateRowsParams p;
+  p.x = x; p.ld = ld; p.positions = positions; p.inv_freq = inv_freq; p.head_dim = head_dim; p.rot_dim = rot_dim;
+  p.rot_scale = rot_scale; p.col[0] = col0; p.col[1] = col1; p.heads[0] = heads0; p.heads[1] = heads1;
+  p.scale[0] = scale0; p.scale[1] = scale1;
+  const int warps = 4;
+  int head_blocks = (heads0 + heads1 + warps - 1) / warps;
+  if (head_blocks > 64) head_blocks = 64;
+  lb::launch(lb::rotate_rows_kernel, dim3(num_tokens, head_blocks), dim3(warps * 32), 0, stream, p);
+  LB_CHECK_LAUNCH("rotate_rows");
+  return 0;
+}
 
 LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const void* v_in,
                          long long q_stride, long long k_stride, long long v_stride, void* q_out,
@@ -205,7 +266,7 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
                          const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
                          int num_tokens, int num_q_heads, int num_kv_heads, int head_dim,
                          int rot_dim, int page_size, int max_pages, float eps, int in_dtype, int v_dim,
-                         cudaStream_t stream) {
+                         float rot_scale, cudaStream_t stream) {
   if (v_dim <= 0) v_dim = head_dim;
   LB_CHECK_ARG(lb::valid_dtype(in_dtype) && v_dim <= 1024, "rope_kv: bad input type or value size");
   LB_CHECK_ARG(lb::valid_dtype(dtype), "rope_kv: bad dtype %d", dtype);
@@ -224,6 +285,7 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
   p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.inv_freq = rot_dim > 0 ? inv_freq : nullptr;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
   p.rot_dim = rot_dim; p.page_size = page_size; p.max_pages = max_pages; p.eps = eps; p.v_dim = v_dim;
+  p.rot_scale = rot_scale;
   const int warps = 4;
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
   // The register version: bfloat16, heads of 64 / 128 / 256, whole head rotated, every row 16-byte aligned.

@@ -4,6 +4,7 @@
 //
 //   delta rule    g = exp(-exp(A_h) softplus(a_t + dt_h))     w = sigmoid(b_t)
 //                 S <- g S;   u = w (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+//                 (rows_decay: g is a vector, one decay for every row r of the state, from a_t[h, r] and dt[h, r]; S <- diag(g) S)
 //   state space   w = softplus(a_t + dt_h)     g = exp(-exp(A_h) w)
 //                 S <- g S + k_t (w v_t)^T;    o_t = S^T q_t + D_h v_t          (k = B, q = C, v = x)
 //
@@ -40,6 +41,7 @@ struct StateRecurrenceParams {
   float q_scale, unit_eps;
   int vec;                       // q, k, v rows start on 16-byte boundaries and hold whole 16-byte pieces
   int svec;                      // so do the state's rows
+  int avec;                      // with a decay for every state row: so do the rows of `a`
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
@@ -53,13 +55,16 @@ __device__ __forceinline__ void sr_cp16(float* dst, const float* src) {
 
 // floats of shared memory: q and k (two buffers of 16 rows of (RPL + 4) * SUB), v, a, b (two buffers), g, w, and the
 // tile that holds the lanes' partial read-outs of a chunk or, at both ends, the CTA's part of the state
-__host__ __device__ constexpr int sr_smem_floats(int rpl, int sub, int tokens) {
+// (with a decay for every state row, two more buffers of 16 rows behind the tile)
+__host__ __device__ constexpr int sr_smem_floats(int rpl, int sub, int tokens, bool rows_decay = false) {
   const int cols = SR_THREADS / sub, row = (rpl + 4) * sub;
   const int tile = tokens * SR_THREADS > rpl * sub * cols ? tokens * SR_THREADS : rpl * sub * cols;
-  return 4 * tokens * row + 2 * tokens * cols + 6 * (tokens < 4 ? 4 : tokens) + tile;
+  return 4 * tokens * row + 2 * tokens * cols + 6 * (tokens < 4 ? 4 : tokens) + tile + (rows_decay ? 2 * tokens * row : 0);
 }
 
-template <bool DELTA, int RPL, int SUB, int TOK>
+// VG: the decay is a vector, one number for every row of the state (key channel) and token: `a` holds heads * dim
+// numbers a token and dt_bias heads * dim, g[r] = exp(-exp(A_h) softplus(a[h, r] + dt[h, r])), and S <- diag(g) S.
+template <bool DELTA, int RPL, int SUB, int TOK, bool VG = false>
 __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecurrenceParams p) {
   constexpr int T = TOK, COLS = SR_THREADS / SUB, ROW = (RPL + 4) * SUB, DP = RPL * SUB;
   extern __shared__ __align__(16) float sr_smem[];
@@ -72,16 +77,20 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
   float* g_s = b_s + 2 * TS;                      // [TS] decay
   float* w_s = g_s + TS;                          // [TS] write strength
   float* o_s = w_s + TS;                          // [T][COLS][SUB] partial read-outs; the state's tile [DP][COLS] at both ends
+  constexpr int TILE = T * SR_THREADS > DP * COLS ? T * SR_THREADS : DP * COLS;
+  float* gv_s = o_s + TILE;                       // VG: [2][T][ROW], laid out as k_s: first the step sizes as fetched, then the decays
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = tid % SUB, col_local = tid / SUB;
   const int h = blockIdx.y, seq = blockIdx.z;
   const int col0 = blockIdx.x * COLS;
   const int grp = h / (p.heads / p.groups);
-  const float A = expf(p.A_log[h]), dtb = p.dt_bias[h];
+  const float A = expf(p.A_log[h]), dtb = VG ? 0.f : p.dt_bias[h];
   const float Dh = p.D ? p.D[h] : 0.f;
-  if (p.dim < DP || col0 + COLS > p.vdim)          // rows past dim and columns past vdim stay zero; nothing else of the buffers is read unwritten
+  if (p.dim < DP || col0 + COLS > p.vdim) {        // rows past dim and columns past vdim stay zero; nothing else of the buffers is read unwritten
     for (int i = tid; i < 4 * T * ROW + 2 * T * COLS; i += SR_THREADS) sr_smem[i] = 0.f;
+    if (VG) for (int i = tid; i < 2 * T * ROW; i += SR_THREADS) gv_s[i] = 0.f;
+  }
   pdl_wait();
   const int first = p.cu_tokens[seq], n = p.cu_tokens[seq + 1] - first;
   float* S = p.state + ((size_t)p.slots[seq] * p.heads + h) * p.dim * p.vdim;
@@ -133,8 +142,23 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
         if (col0 + c < p.vdim) sr_cp4(vb + tt * COLS + c, p.v + (row0 + tt) * p.v_ld + (size_t)h * p.vdim + col0 + c);
       }
     }
+    if (VG) {
+      float* gb = gv_s + buf * T * ROW;
+      if (p.avec) {
+        const int per = p.dim / 4;
+        for (int i = tid; i < nt * per; i += SR_THREADS) {
+          const int tt = i / per, r = (i % per) * 4;
+          sr_cp16(gb + tt * ROW + r + 4 * (r / RPL), p.a + (row0 + tt) * p.a_ld + (size_t)h * p.dim + r);
+        }
+      } else {
+        for (int i = tid; i < nt * p.dim; i += SR_THREADS) {
+          const int tt = i / p.dim, r = i % p.dim;
+          sr_cp4(gb + tt * ROW + r + 4 * (r / RPL), p.a + (row0 + tt) * p.a_ld + (size_t)h * p.dim + r);
+        }
+      }
+    }
     if (tid < nt) {
-      sr_cp4(a_s + buf * TS + tid, p.a + (row0 + tid) * p.a_ld + h);
+      if (!VG) sr_cp4(a_s + buf * TS + tid, p.a + (row0 + tid) * p.a_ld + h);
       if (DELTA) sr_cp4(b_s + buf * TS + tid, p.b + (row0 + tid) * p.b_ld + h);
     }
   };
@@ -152,7 +176,14 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
     float* qb = q_s + buf * T * ROW;
     float* kb = k_s + buf * T * ROW;
     const float* vb = v_s + buf * T * COLS;
-    if (tid < nt) {
+    float* gb = gv_s + buf * T * ROW;
+    if (VG) {
+      for (int i = tid; i < nt * p.dim; i += SR_THREADS) {
+        const int tt = i / p.dim, r = i % p.dim, at = tt * ROW + r + 4 * (r / RPL);
+        gb[at] = expf(-A * softplus_f(gb[at] + p.dt_bias[(size_t)h * p.dim + r]));
+      }
+      if (tid < nt) w_s[tid] = 1.f / (1.f + expf(-b_s[buf * TS + tid]));
+    } else if (tid < nt) {
       const float sp = softplus_f(a_s[buf * TS + tid] + dtb);
       g_s[tid] = expf(-A * sp);
       w_s[tid] = DELTA ? 1.f / (1.f + expf(-b_s[buf * TS + tid])) : sp;
@@ -170,12 +201,19 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float g = g_s[tt], w = w_s[tt], vj = vb[tt * COLS + col_local];
+      const float g = VG ? 1.f : g_s[tt], w = w_s[tt], vj = vb[tt * COLS + col_local];
       float kk[RPL], qq[RPL];
 #pragma unroll
       for (int i = 0; i < RPL; i += 4) {
         *reinterpret_cast<float4*>(kk + i) = *reinterpret_cast<const float4*>(kb + tt * ROW + sub * (RPL + 4) + i);
         *reinterpret_cast<float4*>(qq + i) = *reinterpret_cast<const float4*>(qb + tt * ROW + sub * (RPL + 4) + i);
+      }
+      if (VG) {                                    // every row decays by its own factor first; the rest is the rule with g = 1
+#pragma unroll
+        for (int i = 0; i < RPL; i += 4) {
+          const float4 g4 = *reinterpret_cast<const float4*>(gb + tt * ROW + sub * (RPL + 4) + i);
+          s[i] *= g4.x; s[i + 1] *= g4.y; s[i + 2] *= g4.z; s[i + 3] *= g4.w;
+        }
       }
       float u;
       if (DELTA) {
@@ -233,13 +271,14 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
 // Norm in equal groups of a row with a gate, after a recurrence:
 //   gate_first = 0:  out = y / rms_group(y) * w * act(gate)           (the gated delta rule: a group is a head)
 //   gate_first = 1:  z = y * act(gate);  out = z / rms_group(z) * w     (Mamba-2: the gate comes before the norm)
-// w has `wn` entries and is read at column % wn (wn = the group's size: one weight shared by the groups).
+// w has `wn` entries and is read at column % wn (wn = the group's size: one weight shared by the groups); no w: no weight.
+// y may come in `planes` planes, `plane` elements apart, whose sum is meant (a recurrence whose CTAs share out a state's rows).
 // act: 0 silu, 1 sigmoid.  One to eight warps a (row, group), by the group's size, and as many groups of a row in a CTA
 // (threadIdx.y) as make it 256 threads; a group's warps add their sums of squares in warp order.
 template <typename TO>
 __global__ void gated_group_norm_kernel(TO* __restrict__ out, long long out_ld, const float* __restrict__ y, long long y_ld,
                                         const float* __restrict__ gate, long long gate_ld, const float* __restrict__ w, int wn,
-                                        int n, int groups, int gate_first, int act, float eps, float scale) {
+                                        int n, int groups, int gate_first, int act, float eps, float scale, int planes, long long plane) {
   __shared__ float part[8][8];
   pdl_trigger();
   pdl_wait();
@@ -248,9 +287,14 @@ __global__ void gated_group_norm_kernel(TO* __restrict__ out, long long out_ld, 
   const int gs = g < groups ? n / groups : 0;      // a group past the last has no columns, but meets the others at the barrier
   const float* yr = y + (size_t)t * y_ld + (size_t)g * gs;
   const float* gr = gate + (size_t)t * gate_ld + (size_t)g * gs;
+  auto value = [&](int c) {                        // y may come in planes whose sum, in order, is meant
+    float v = yr[c];
+    for (int q = 1; q < planes; ++q) v += yr[(size_t)q * plane + c];
+    return v;
+  };
   float ss = 0.f;
   for (int c = threadIdx.x; c < gs; c += blockDim.x) {
-    float x = yr[c];
+    float x = value(c);
     if (gate_first) {
       const float z = gr[c];
       x *= act == 0 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));
@@ -267,8 +311,9 @@ __global__ void gated_group_norm_kernel(TO* __restrict__ out, long long out_ld, 
     const int col = g * gs + c;
     const float z = gr[c];
     const float a = act == 0 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));
-    const float x = yr[c];
-    const float r = gate_first ? (x * a) * inv * w[col % wn] : x * inv * w[col % wn] * a;
+    const float x = value(c);
+    const float wc = w ? w[col % wn] : 1.f;
+    const float r = gate_first ? (x * a) * inv * wc : x * inv * wc * a;
     out[(size_t)t * out_ld + col] = from_f32<TO>(r * scale);
   }
 }
@@ -279,7 +324,9 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
                                   long long v_ld, const float* a, long long a_ld, const float* b, long long b_ld,
                                   const float* A_log, const float* dt_bias, const float* D, float* state, float* out,
                                   long long out_ld, const int* cu_tokens, const int* slots, int num_seqs, int heads, int groups,
-                                  int dim, int vdim, int unit_norm, float q_scale, float unit_eps, int single_tokens, cudaStream_t stream) {
+                                  int dim, int vdim, int unit_norm, float q_scale, float unit_eps, int single_tokens, int rows_decay,
+                                  cudaStream_t stream) {
+  LB_CHECK_ARG(!rows_decay || delta, "state_recurrence: a decay for every state row comes with the delta rule");
   LB_CHECK_ARG(q && k && v && a && A_log && dt_bias && state && out && cu_tokens && slots && (!delta || b),
                "state_recurrence: null argument");
   LB_CHECK_ARG(heads > 0 && groups > 0 && heads % groups == 0, "state_recurrence: %d heads are not a multiple of %d groups", heads, groups);
@@ -294,6 +341,7 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
   auto aligned = [](const float* x, long long ld) { return ((uintptr_t)x % 16 == 0) && ld % 4 == 0; };
   p.vec = dim % 4 == 0 && vdim % 4 == 0 && aligned(q, q_ld) && aligned(k, k_ld) && aligned(v, v_ld);
   p.svec = vdim % 4 == 0 && (uintptr_t)state % 16 == 0;
+  p.avec = rows_decay && dim % 4 == 0 && aligned(a, a_ld);
 #define LB_SR1(RPL, SUB, TOK)                                                                                       \
   do {                                                                                                              \
     const size_t smem = (size_t)lb::sr_smem_floats(RPL, SUB, TOK) * sizeof(float);                                  \
@@ -304,7 +352,15 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
       cfg = true;                                                                                                   \
     }                                                                                                               \
     dim3 grid((vdim + lb::SR_THREADS / SUB - 1) / (lb::SR_THREADS / SUB), heads, num_seqs), block(lb::SR_THREADS); \
-    if (delta) lb::launch(lb::state_recurrence_kernel<true, RPL, SUB, TOK>, grid, block, smem, stream, p);          \
+    if (rows_decay) {                                                                                               \
+      const size_t smem_g = (size_t)lb::sr_smem_floats(RPL, SUB, TOK, true) * sizeof(float);                        \
+      static bool cfg_g = false;                                                                                    \
+      if (!cfg_g) {                                                                                                 \
+        cudaFuncSetAttribute(lb::state_recurrence_kernel<true, RPL, SUB, TOK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_g); \
+        cfg_g = true;                                                                                               \
+      }                                                                                                             \
+      lb::launch(lb::state_recurrence_kernel<true, RPL, SUB, TOK, true>, grid, block, smem_g, stream, p);           \
+    } else if (delta) lb::launch(lb::state_recurrence_kernel<true, RPL, SUB, TOK>, grid, block, smem, stream, p);          \
     else lb::launch(lb::state_recurrence_kernel<false, RPL, SUB, TOK>, grid, block, smem, stream, p);               \
   } while (0)
   // a step of single tokens stages one token at a time: the same sums in the same order, a fifth of the shared memory
@@ -325,9 +381,9 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
 
 LB_EXPORT int lb_gated_group_norm(void* out, int out_dtype, long long out_ld, const float* y, long long y_ld, const float* gate,
                                   long long gate_ld, const float* w, int wn, int num_rows, int n, int groups, int gate_first,
-                                  int act, float eps, float scale, cudaStream_t stream) {
-  LB_CHECK_ARG(lb::valid_dtype(out_dtype), "gated_group_norm: bad dtype");
-  LB_CHECK_ARG(out && y && gate && w && num_rows >= 0 && n > 0 && groups > 0 && n % groups == 0 && wn > 0 && (act == 0 || act == 1),
+                                  int act, float eps, float scale, int planes, long long plane, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(out_dtype) && planes >= 1, "gated_group_norm: bad dtype or plane count");
+  LB_CHECK_ARG(out && y && gate && num_rows >= 0 && n > 0 && groups > 0 && n % groups == 0 && (!w || wn > 0) && (act == 0 || act == 1),
                "gated_group_norm: bad arguments rows=%d n=%d groups=%d", num_rows, n, groups);
   if (num_rows == 0) return 0;
   LB_CHECK_ARG(groups <= 65535, "gated_group_norm: %d groups", groups);
@@ -338,7 +394,7 @@ LB_EXPORT int lb_gated_group_norm(void* out, int out_dtype, long long out_ld, co
   LB_CHECK_ARG((groups + per_cta - 1) / per_cta <= 65535, "gated_group_norm: %d groups", groups);
   LB_DISPATCH_DTYPE(out_dtype, TO, {
     lb::launch(lb::gated_group_norm_kernel<TO>, dim3(num_rows, (groups + per_cta - 1) / per_cta), dim3(warps * 32, per_cta), 0, stream,
-               (TO*)out, out_ld, y, y_ld, gate, gate_ld, w, wn, n, groups, gate_first, act, eps, scale);
+               (TO*)out, out_ld, y, y_ld, gate, gate_ld, w, wn > 0 ? wn : 1, n, groups, gate_first, act, eps, scale, planes, plane);
   })
   LB_CHECK_LAUNCH("gated_group_norm");
   return 0;

@@ -91,13 +91,14 @@ LB_EXPORT int lb_swiglu(int dtype, void* out, const void* gate, const void* up, 
 }
 
 // Activations of a feed-forward without a gate, out = act(x), computed in 32-bit and rounded once.  `act`:
-// 0 silu, 1 relu, 2 the tanh form of gelu, 4 xIELU with its two positive numbers a_p, a_n (p0, p1):
+// 0 silu, 1 relu, 2 the tanh form of gelu, 5 the square of relu, 4 xIELU with its two positive numbers a_p, a_n (p0, p1):
 //   x > 0: a_p x^2 + x / 2        x <= 0: a_n (exp(x) - 1 - x) + x / 2
 // (the design's learned numbers p, q enter as a_p = softplus(p), a_n = 1/2 + softplus(q), formed once on the host).
 namespace lb {
 
 __device__ __forceinline__ float plain_act(int act, float p0, float p1, float x) {
   if (act == 4) return x > 0.f ? fmaf(p0 * x, x, 0.5f * x) : fmaf(p1, expm1f(x) - x, 0.5f * x);
+  if (act == 5) { const float r = fmaxf(x, 0.f); return r * r; }
   return gated_act(act, 0.f, x, 1.f);
 }
 
@@ -140,7 +141,8 @@ LB_EXPORT int lb_activation(int dtype, void* out, const void* x, long long in_st
                             float p1, cudaStream_t stream) {
   LB_CHECK_ARG(lb::valid_dtype(dtype), "activation: bad dtype %d", dtype);
   LB_CHECK_ARG(out && x && num_tokens >= 0 && n > 0 && in_stride >= n, "activation: bad sizes");
-  LB_CHECK_ARG(act == 0 || act == 1 || act == 2 || act == 4, "activation: %d is none of silu (0), relu (1), gelu_tanh (2), xielu (4)", act);
+  LB_CHECK_ARG(act == 0 || act == 1 || act == 2 || act == 4 || act == 5,
+               "activation: %d is none of silu (0), relu (1), gelu_tanh (2), xielu (4), relu squared (5)", act);
   if (num_tokens == 0) return 0;
   const long long total = (long long)num_tokens * n;
   if (dtype == LB_BF16 && n % 8 == 0 && in_stride % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
@@ -156,5 +158,31 @@ LB_EXPORT int lb_activation(int dtype, void* out, const void* x, long long in_st
     lb::launch(lb::activation_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out, (const T*)x, in_stride, n, total, act, p0, p1);
   })
   LB_CHECK_LAUNCH("activation");
+  return 0;
+}
+
+// out[t, :n] = x[t, :n] (32-bit rows that may be a column range of a wider matrix) rounded to out's type, out rows
+// contiguous: what a product with 32-bit output left, as the input of a second product.
+namespace lb {
+template <typename TO>
+__global__ void round_cols_kernel(TO* __restrict__ out, const float* __restrict__ x, long long x_ld, int n, long long total) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / n;
+    out[idx] = from_f32<TO>(x[t * x_ld + (idx - t * n)]);
+  }
+}
+}  // namespace lb
+
+LB_EXPORT int lb_round_cols(void* out, int out_dtype, const float* x, long long x_ld, int num_rows, int n, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(out_dtype) && out && x && num_rows >= 0 && n > 0 && x_ld >= n, "round_cols: bad arguments");
+  if (num_rows == 0) return 0;
+  const long long total = (long long)num_rows * n;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  LB_DISPATCH_DTYPE(out_dtype, TO, {
+    lb::launch(lb::round_cols_kernel<TO>, dim3(blocks), dim3(256), 0, stream, (TO*)out, x, x_ld, n, total);
+  })
+  LB_CHECK_LAUNCH("round_cols");
   return 0;
 }

@@ -39,9 +39,14 @@ def build_runner(model_dir: str | Path, options: Optional[EngineOptions] = None,
     arch = resolve_architecture(cfg_dict)
     cfg = arch.config_from_dict(cfg_dict)
     rt = _runtime(options)
-    model = arch.build(cfg, rt)
     source = CheckpointFolder(model_dir)
     try:
+        # A design may leave sizes to the shapes of its tensors (the rank of a low-rank map, say): its configuration
+        # then offers with_tensor_shapes(shape_of), which fills them in from the checkpoint before the model is composed.
+        if hasattr(cfg, "with_tensor_shapes"):
+            have = set(source.names())
+            cfg = cfg.with_tensor_shapes(lambda name: tuple(source.shape_dtype(name)[0]) if name in have else None)
+        model = arch.build(cfg, rt)
         bind_weights(model, source, rt.act_dtype, rt.device)
     finally:
         source.close()

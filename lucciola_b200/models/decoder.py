@@ -2,7 +2,9 @@
 
 `calls` gives the order in which blocks run.  A call names a block and a cache; a block may be
 called twice (with two caches), and a call may read a cache that an earlier call has written
-(`write_cache=False`): then the mixer computes queries only and attends to what is there.
+(`write_cache=False`): then the mixer computes queries only and attends to what is there.  A call may ask for the
+embedding's output to be added to the stream before its block runs (`add_embedding`: models that repeat a run of
+layers and feed the input in again at the start of every pass).
 """
 from __future__ import annotations
 
@@ -11,6 +13,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..parts.base import Block, KVPages, Norm, Part, Runtime, StateSlot, StepContext, StreamCopy
 from ..parts.embedding import OutputHead, TokenEmbedding
 
@@ -20,6 +23,7 @@ class LayerCall:
     block: int
     cache: int
     write_cache: bool = True
+    add_embedding: bool = False      # the embedding's output is added to the stream before this call's block runs
 
 
 class DecoderModel(Part):
@@ -69,15 +73,37 @@ class DecoderModel(Part):
     def forward(self, token_ids: torch.Tensor, step: StepContext, caches: Sequence[object],
                 logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the tokens of one step; float32 logits [R, vocab] for the rows asked for (None if none)."""
-        residual = self.embedding.forward(token_ids, step.positions) if getattr(self.embedding, "uses_positions", False) else self.embedding.forward(token_ids)
+        again = None                                     # a second copy of the embedding's output, for the calls that add it
+        if any(c.add_embedding for c in self.calls):
+            again = self.rt.empty((token_ids.shape[0], self.embedding.hidden_size), torch.float32)
+        pos = step.positions if getattr(self.embedding, "uses_positions", False) else None
+        residual = self.embedding.forward(token_ids, pos, copy=again) if again is not None else (
+            self.embedding.forward(token_ids, pos) if pos is not None else self.embedding.forward(token_ids))
         delta = None
         for i, c in enumerate(self.calls):
+            if c.add_embedding:
+                # with what the block before left, if this block's first norm adds two things in its pass; else by itself
+                if self.blocks[c.block].takes_delta_parts and (delta is None or (torch.is_tensor(delta) and delta.dtype == again.dtype)):
+                    delta = (delta, again) if delta is not None else (again,)
+                else:
+                    if isinstance(delta, tuple):
+                        for d in delta:
+                            ops.add_into(residual, d, self.rt.stream)
+                        delta = None
+                    elif torch.is_tensor(delta):
+                        ops.add_into(residual, delta, self.rt.stream)
+                        delta = None
+                    elif delta is not None and not isinstance(delta, StreamCopy):
+                        raise ops.KernelError("the embedding cannot be added again behind a block that hands its output on inside a product")
+                    ops.add_into(residual, again, self.rt.stream)
+                    delta = None
             # what the call after this one offers to take over from this one's last product (see Block.entry_sink)
             nxt = self.calls[i + 1] if i + 1 < len(self.calls) else None
             block = self.blocks[c.block]
             if isinstance(delta, StreamCopy) and not block.takes_stream_copy:
                 delta = None                             # nothing is left to be added; this block makes its own input
-            next_sink = self.blocks[nxt.block].entry_sink(residual, step.num_tokens, nxt.write_cache) if nxt is not None else None
+            next_sink = (self.blocks[nxt.block].entry_sink(residual, step.num_tokens, nxt.write_cache)
+                         if nxt is not None and not nxt.add_embedding else None)
             # a block whose sublayers run side by side may leave their outputs unsummed when the norm that adds them
             # to the residual stream takes both (see Block.offers_delta_parts)
             parts_ok = (self.blocks[nxt.block].takes_delta_parts if nxt is not None else self.final_norm.takes_delta_parts)

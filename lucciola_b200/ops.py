@@ -30,13 +30,14 @@ def dtype_code(dt: torch.dtype) -> int:
 
 
 _SIGNATURES = {
-    "lb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "lb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p,
+                     c_void_p],
     "lb_layernorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "lb_layernorm_add": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_float, c_float, c_void_p, c_int,
                          c_int, c_int, c_void_p],
     "lb_round_copy": [c_void_p, c_int, c_void_p, c_longlong, c_void_p],
     "lb_decay_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p],
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_void_p],
     "lb_rmsnorm_gated": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_float, c_int, c_int,
                          c_int, c_longlong, c_void_p],
     "lb_head_gate": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_int, c_void_p],
@@ -66,18 +67,21 @@ _SIGNATURES = {
     "lb_add_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "lb_rope_kv": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p],
+    "lb_rotate_rows": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_float, c_int, c_int,
+                       c_float, c_void_p],
+    "lb_round_cols": [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p],
     "lb_attention_plain": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_float, c_void_p, c_int,
-                           c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "lb_short_conv": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_int, c_int, c_int, c_int, c_void_p],
     "lb_short_conv_state": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lb_state_recurrence": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                             c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
-                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p],
     "lb_gated_group_norm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int,
-                            c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_longlong, c_void_p],
     "lb_bias_rmsnorm_cols": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
     "lb_pool_kv": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -99,7 +103,7 @@ _SIGNATURES = {
                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
     "lb_attention_flash_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p,
-                              c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+                              c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -156,10 +160,14 @@ def current_stream() -> int:
 
 def embedding(out: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, stream: int,
               pos_table: torch.Tensor | None = None, positions: torch.Tensor | None = None,
-              sin_freq: torch.Tensor | None = None) -> None:
-    """out[t, :] = table[ids[t], :] as float32; with a table of position vectors, + pos_table[positions[t], :]; with
+              sin_freq: torch.Tensor | None = None, scale: float = 1.0, copy: torch.Tensor | None = None) -> None:
+    """out[t, :] = table[ids[t], :] * scale as float32; with a table of position vectors, + pos_table[positions[t], :]; with
     `sin_freq` (float64 [ceil(H / 2)]) instead + the sinusoidal vector whose entries 2i, 2i + 1 are the sine and
-    cosine of positions[t] * sin_freq[i]."""
+    cosine of positions[t] * sin_freq[i].  `copy` (float32, out's shape) receives the same rows a second time."""
+    if copy is not None:
+        _check(copy, "embedding copy", torch.float32)
+        if copy.shape != out.shape:
+            raise KernelError("the embedding's second copy has the first one's shape")
     _check(out, "embedding output", torch.float32); _check(ids, "token ids", torch.int32); _check(table, "embedding table")
     T, H = out.shape
     if sin_freq is not None:
@@ -171,7 +179,8 @@ def embedding(out: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, stream:
         if pos_table.shape[1] != H:
             raise KernelError(f"position vectors have {pos_table.shape[1]} values, the embedding {H}")
     _call("lb_embedding", out.data_ptr(), ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), T, H,
-          table.shape[0], _ptr(pos_table), _ptr(positions), pos_table.shape[0] if pos_table is not None else 0, _ptr(sin_freq), stream)
+          table.shape[0], _ptr(pos_table), _ptr(positions), pos_table.shape[0] if pos_table is not None else 0, _ptr(sin_freq),
+          float(scale), _ptr(copy), stream)
 
 
 def add_group_rmsnorm(out: torch.Tensor, residual: torch.Tensor, deltas: tuple, weight: torch.Tensor, groups: int,
@@ -298,12 +307,12 @@ def rope_kv(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, q_out: t
             inv_freq: torch.Tensor | None = None, rot_dim: int = 0,
             k_cache: torch.Tensor | None = None, v_cache: torch.Tensor | None = None,
             token_seq: torch.Tensor | None = None, block_table: torch.Tensor | None = None, page_size: int = 0,
-            k_out: torch.Tensor | None = None, v_out: torch.Tensor | None = None, v_dim: int = 0) -> None:
+            k_out: torch.Tensor | None = None, v_out: torch.Tensor | None = None, v_dim: int = 0, rot_scale: float = 1.0) -> None:
     """Per-head norm of q and k, rotation, and the write of k and v into pages (or into k_out, v_out).
 
     q_in, k_in and v_in are 2-d views whose rows may be column ranges of one wider matrix; they may be float32 where
     the heads are stored in bfloat16 (a product with 32-bit output).  `v_dim`: the size of a value head if it is not
-    head_dim (the value pool then has rows of that size)."""
+    head_dim (the value pool then has rows of that size).  `rot_scale` multiplies the rotation's sines and cosines."""
     T = q_in.shape[0]
     dt = q_out.dtype
     for t, w in ((q_in, "q"), (k_in, "k"), (v_in, "v")):
@@ -318,7 +327,31 @@ def rope_kv(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, q_out: t
     _call("lb_rope_kv", dtype_code(dt), q_in.data_ptr(), k_in.data_ptr(), v_in.data_ptr(), q_in.stride(0),
           k_in.stride(0), v_in.stride(0), q_out.data_ptr(), _ptr(k_out), _ptr(v_out), _ptr(k_cache), _ptr(v_cache),
           positions.data_ptr(), _ptr(token_seq), _ptr(block_table), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
-          T, num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages, eps, dtype_code(q_in.dtype), v_dim, stream)
+          T, num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages, eps, dtype_code(q_in.dtype), v_dim, float(rot_scale), stream)
+
+
+def rotate_rows(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None, head_dim: int, rot_dim: int, ranges,
+                stream: int, rot_scale: float = 1.0) -> None:
+    """Rotation in place of 32-bit rows: `ranges` is one or two (first column, heads, scale); each range holds `heads`
+    heads of `head_dim` whose first rot_dim entries are rotated (halves paired, angle position * inv_freq[i], sines
+    and cosines times rot_scale) and whose every entry is then multiplied by `scale`."""
+    _rows32(x, "rows to rotate"); _check(positions, "positions", torch.int32)
+    if inv_freq is not None:
+        _check(inv_freq, "frequencies", torch.float32)
+    rs = list(ranges)
+    if not 1 <= len(rs) <= 2 or any(c < 0 or c + h * head_dim > x.shape[1] for c, h, _ in rs):
+        raise KernelError("one or two column ranges inside the rows")
+    (c0, h0, s0), (c1, h1, s1) = rs[0], (rs[1] if len(rs) > 1 else (0, 0, 1.0))
+    _call("lb_rotate_rows", x.data_ptr(), x.stride(0), x.shape[0], positions.data_ptr(), _ptr(inv_freq), head_dim, rot_dim,
+          float(rot_scale), c0, h0, float(s0), c1, h1, float(s1), stream)
+
+
+def round_cols(out: torch.Tensor, x: torch.Tensor, stream: int) -> None:
+    """out (contiguous, any type) = the 32-bit rows x (a column range allowed), rounded."""
+    _check(out, "rounded copy"); _rows32(x, "rows to round")
+    if out.shape != x.shape:
+        raise KernelError("a rounded copy has its source's shape")
+    _call("lb_round_cols", out.data_ptr(), dtype_code(out.dtype), x.data_ptr(), x.stride(0), x.shape[0], x.shape[1], stream)
 
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -326,8 +359,9 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
                     stream: int, v_dim: int = 0, slopes: torch.Tensor | None = None, softcap: float = 0.0,
                     sinks: torch.Tensor | None = None, pool: int = 0, pool_k: torch.Tensor | None = None,
-                    pool_v: torch.Tensor | None = None, pool_table: torch.Tensor | None = None) -> None:
-    """`v_dim`: the size of a value head if it is not head_dim (out is then [T, heads, v_dim]); `slopes` (float32
+                    pool_v: torch.Tensor | None = None, pool_table: torch.Tensor | None = None, chunk: int = 0) -> None:
+    """`chunk` = C > 0: the query at position i sees the keys floor(i / C) * C .. i only.
+    `v_dim`: the size of a value head if it is not head_dim (out is then [T, heads, v_dim]); `slopes` (float32
     [heads]): the score of key j for the query at position i is lowered by slopes[h] * (i - j).  `softcap` > 0: scores
     become softcap * tanh(score / softcap).  `sinks` (float32 [heads]): exp(sinks[h]) joins the softmax's denominator.
     `pool` = P > 0 with a window: the query at i also sees entry b of the pooled cache (pool_k, pool_v through
@@ -346,7 +380,7 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
           positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), q.shape[0], num_q_heads, num_kv_heads,
           head_dim, page_size, block_table.shape[1], window, scale, v_dim, _ptr(slopes), softcap, _ptr(sinks), pool,
           _ptr(pool_k) if pool else None, _ptr(pool_v) if pool else None, _ptr(pool_table) if pool else None,
-          pool_table.shape[1] if pool else 0, stream)
+          pool_table.shape[1] if pool else 0, int(chunk), stream)
 
 
 def _rows32(t: torch.Tensor, what: str) -> None:
@@ -383,11 +417,12 @@ def short_conv_state(state: torch.Tensor, x: torch.Tensor, taps: int, step, stre
 def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None,
                      A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
                      step, heads: int, groups: int, dim: int, vdim: int, stream: int, delta: bool, unit_norm: bool = False,
-                     q_scale: float = 1.0, unit_eps: float = 1e-6) -> None:
+                     q_scale: float = 1.0, unit_eps: float = 1e-6, rows_decay: bool = False) -> None:
     """A recurrence with a decay and a write strength per token over this step's tokens (csrc/state_recurrence.cu):
     delta=True the gated delta rule (b: beta's input), else the state space of Mamba-2 (k = B, q = C, v = x, a = dt's
     input, D optional).  q, k [T, groups * dim], v [T, heads * vdim], a, b [T, heads]: float32 rows, column ranges allowed;
-    state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32."""
+    state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32.
+    `rows_decay` (delta rule only): a decay for every row of the state; a is then [T, heads * dim] and dt_bias [heads * dim]."""
     for t, w in ((q, "q"), (k, "k"), (v, "v"), (a, "a")) + (((b, "b"),) if b is not None else ()):
         _rows32(t, w)
     _rows32(out, "recurrence output")
@@ -396,26 +431,36 @@ def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch
         _check(D, "D", torch.float32)
     T = q.shape[0]
     if (tuple(q.shape) != (T, groups * dim) or tuple(k.shape) != (T, groups * dim) or tuple(v.shape) != (T, heads * vdim)
-            or tuple(a.shape) != (T, heads) or tuple(out.shape) != (T, heads * vdim) or tuple(state.shape[1:]) != (heads, dim, vdim)):
+            or tuple(a.shape) != (T, heads * dim if rows_decay else heads) or dt_bias.numel() != (heads * dim if rows_decay else heads)
+            or tuple(out.shape) != (T, heads * vdim) or tuple(state.shape[1:]) != (heads, dim, vdim)):
         raise KernelError("the recurrence's operands do not fit its head counts and sizes")
     _call("lb_state_recurrence", 1 if delta else 0, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
           a.data_ptr(), a.stride(0), _ptr(b), b.stride(0) if b is not None else 0, A_log.data_ptr(), dt_bias.data_ptr(), _ptr(D),
           state.data_ptr(), out.data_ptr(), out.stride(0), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs,
-          heads, groups, dim, vdim, 1 if unit_norm else 0, q_scale, unit_eps, 1 if T == step.num_seqs else 0, stream)
+          heads, groups, dim, vdim, 1 if unit_norm else 0, q_scale, unit_eps, 1 if T == step.num_seqs else 0, 1 if rows_decay else 0, stream)
 
 
-def gated_group_norm(out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
+def gated_group_norm(out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, groups: int, eps: float,
                      stream: int, gate_first: bool = False, act: str = "silu", scale: float = 1.0) -> None:
     """The norm behind a recurrence, in `groups` equal parts of a row, with a gate: out = y / rms_part(y) * w * act(gate),
     or with gate_first z = y * act(gate), out = z / rms_part(z) * w.  y, gate: float32 rows (column ranges allowed); weight
-    float32 of the row's size, or of a part's size (then shared by the parts); out rows of any type."""
-    _rows32(y, "norm input"); _rows32(gate, "gate"); _check(weight, "norm weight", torch.float32)
+    float32 of the row's size, or of a part's size (then shared by the parts), or None for a norm without one; out rows of
+    any type.  y may also be [planes, T, n] (contiguous): the sum of the planes, added in order, is meant."""
+    planes, plane = 1, 0
+    if y.dim() == 3:
+        _check(y, "norm input", torch.float32)
+        planes, plane = y.shape[0], y.shape[1] * y.shape[2]
+        y = y[0]
+    _rows32(y, "norm input"); _rows32(gate, "gate")
+    if weight is not None:
+        _check(weight, "norm weight", torch.float32)
     T, n = y.shape
-    if out.stride(1) != 1 or tuple(out.shape) != (T, n) or tuple(gate.shape) != (T, n) or n % groups or weight.numel() not in (n, n // groups):
+    if (out.stride(1) != 1 or tuple(out.shape) != (T, n) or tuple(gate.shape) != (T, n) or n % groups
+            or (weight is not None and weight.numel() not in (n, n // groups))):
         raise KernelError("the gated norm's operands do not fit")
     _call("lb_gated_group_norm", out.data_ptr(), dtype_code(out.dtype), out.stride(0), y.data_ptr(), y.stride(0), gate.data_ptr(),
-          gate.stride(0), weight.data_ptr(), weight.numel(), T, n, groups, 1 if gate_first else 0, {"silu": 0, "sigmoid": 1}[act],
-          eps, scale, stream)
+          gate.stride(0), _ptr(weight), weight.numel() if weight is not None else 0, T, n, groups, 1 if gate_first else 0,
+          {"silu": 0, "sigmoid": 1}[act], eps, scale, planes, plane, stream)
 
 
 def bias_rmsnorm_cols(x: torch.Tensor, ranges, eps: float, stream: int) -> None:
@@ -476,7 +521,7 @@ def rmsnorm_mix2(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, w_a: torch
 
 
 # Activations of a feed-forward without a gate (csrc/swiglu.cu, lb_activation).
-PLAIN_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "xielu": 4}
+PLAIN_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "xielu": 4, "relu2": 5}         # relu2: the square of relu
 
 
 def activation(out: torch.Tensor, x: torch.Tensor, act: str, stream: int, p0: float = 0.0, p1: float = 0.0) -> None:
@@ -727,9 +772,9 @@ def decay_row_split(num_seqs: int, heads: int, dim: int, vdim: int, max_tokens_a
 
 def decay_recurrence(pre: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
                      out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int, max_tokens_a_seq: int = 0,
-                     row_split: int = 0) -> None:
+                     row_split: int = 0, act: bool = True) -> None:
     """Linear attention with a fixed decay per head over this step's tokens: S <- decay_h S + k v^T, out = S^T q with
-    q, k, v = silu of the columns of `pre` (float32, row-strided) at q_col, k_col, v_col; state [slots + 1, heads, dim, vdim]
+    q, k, v = silu of the columns of `pre` (float32, row-strided) at q_col, k_col, v_col (act=False: the columns as they are); state [slots + 1, heads, dim, vdim]
     float32 is read and written at each sequence's slot; out [T, heads * vdim] float32.
     `row_split` >= 1 (see decay_row_split): the outputs of 16 tokens at a time are formed from the state before them
     and the tokens' own scores (32-bit, outputs equal within rounding, several times faster), the state's rows shared out
@@ -743,7 +788,7 @@ def decay_recurrence(pre: torch.Tensor, q_col: int, k_col: int, v_col: int, deca
         raise KernelError(f"the recurrence's output has the wrong shape {tuple(out.shape)}")
     _call("lb_decay_recurrence", pre.data_ptr(), pre.stride(0), q_col, k_col, v_col, decay.data_ptr(), state.data_ptr(),
           out.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs, heads, dim, vdim,
-          max_tokens_a_seq, row_split, T * heads * vdim, stream)
+          max_tokens_a_seq, row_split, T * heads * vdim, 1 if act else 0, stream)
 
 
 def rmsnorm_gated(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, scale: float, eps: float,
@@ -1006,7 +1051,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                     splits: int, stream: int, force_workspace: bool = False, tma: bool = True, kv_share: int = 1,
                     slopes: torch.Tensor | None = None, softcap: float = 0.0, sinks: torch.Tensor | None = None, pool: int = 0,
                     pool_k: torch.Tensor | None = None, pool_v: torch.Tensor | None = None,
-                    pool_table: torch.Tensor | None = None) -> None:
+                    pool_table: torch.Tensor | None = None, chunk: int = 0) -> None:
     """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0).
     `kv_share` > 1: the pools hold num_kv_heads / kv_share heads, and kv head j of this call reads pool head j // kv_share
     (many query heads on one cached head, cut into groups of at most 16 so that decoded tokens fit the decode kernel's tiles).
@@ -1014,8 +1059,9 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     kernel even where a cluster could combine them.  Tiles of at most 16 query rows (decoded tokens) over pages of
     8 to 128 tokens run in the kernel whose keys and values a warp of its own fetches by TMA; `tma=False` keeps them
     in the kernel that fetches with 16-byte copies, which takes every page size.  `softcap`, `sinks` and `pool` (with
-    pool_k, pool_v, pool_table) as in attention_plain; a launch with any of them runs in the kernel with 16-byte copies."""
-    if softcap > 0 or sinks is not None or pool:
+    pool_k, pool_v, pool_table) and `chunk` as in attention_plain; a launch with any of them runs in the kernel with
+    16-byte copies."""
+    if softcap > 0 or sinks is not None or pool or chunk:
         tma = False
     if sinks is not None:
         _check(sinks, "sinks", torch.float32)
@@ -1039,7 +1085,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
           page_size, block_table.shape[1], k_cache.shape[0] if tma else 0, window, scale,
           -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, kv_share, _ptr(slopes), softcap, _ptr(sinks),
           pool, _ptr(pool_k) if pool else None, _ptr(pool_v) if pool else None, _ptr(pool_table) if pool else None,
-          pool_table.shape[1] if pool else 0, stream)
+          pool_table.shape[1] if pool else 0, int(chunk), stream)
 
 
 def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
@@ -1098,7 +1144,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
               num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
               stream: int, plan=None, kv_share: int = 1, v_dim: int = 0, slopes: torch.Tensor | None = None,
               softcap: float = 0.0, sinks: torch.Tensor | None = None, pool: int = 0, pool_k: torch.Tensor | None = None,
-              pool_v: torch.Tensor | None = None, pool_group: int = -1) -> None:
+              pool_v: torch.Tensor | None = None, pool_group: int = -1, chunk: int = 0) -> None:
     """Causal attention of this step's queries over the pages of their requests.  With a `plan` (tile lists
     by kind on the device, see parts/attention.py) the tensor-core kernels run where their conditions hold:
     portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
@@ -1106,19 +1152,22 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     `kv_share` > 1: the plan's lists other than "big" were made for groups of num_q_heads / (num_kv_heads * kv_share)
     query heads, kv_share of which read one cached head (see attention_flash).  A capped score (`softcap`), sinks and
     pooled blocks behind the window (`pool` tokens a block, their means in pool_k / pool_v, pages of group `pool_group`)
-    run in the mma.sync kernel with 16-byte copies, for portions and for decoded tokens, or in the plain kernel."""
-    extras = softcap > 0 or sinks is not None or pool > 0
+    and chunks (`chunk` = C: a query sees the keys of its own run of C positions only) run in the mma.sync kernel with
+    16-byte copies, for portions and for decoded tokens, or in the plain kernel."""
+    extras = softcap > 0 or sinks is not None or pool > 0 or chunk > 0
     pool_table = step.block_tables[pool_group] if pool else None
     if (plan is None or (v_dim and v_dim != head_dim) or ((slopes is not None or extras) and not scale > 0)
             or (pool and kv_share != 1) or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim)):
         # value heads of another size than the keys' are the plain kernel's alone
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream, v_dim=v_dim, slopes=slopes,
-                        softcap=softcap, sinks=sinks, pool=pool, pool_k=pool_k, pool_v=pool_v, pool_table=pool_table)
+                        softcap=softcap, sinks=sinks, pool=pool, pool_k=pool_k, pool_v=pool_v, pool_table=pool_table, chunk=chunk)
         return
     meta, most_rows = plan.arrays, plan.host["rows"]
     longest = step.span_hint or step.max_context_len                 # a recorded step plans for a bucket of lengths
     span = min(longest, window + step.max_q_len) if window > 0 else longest
+    if chunk:
+        span = min(span, chunk)
     if pool:
         span += -(-max(longest - window, 0) // pool)                 # one entry a block behind the window
     kinds = ["all"]
@@ -1137,4 +1186,5 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         splits = attention_splits(tiles.shape[0], num_kv_heads * kv_share, span, rows, wide_clusters=wide)
         attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, rows,
                         num_q_heads, num_kv_heads * kv_share, head_dim, page_size, window, scale, splits, stream, kv_share=kv_share,
-                        slopes=slopes, softcap=softcap, sinks=sinks, pool=pool, pool_k=pool_k, pool_v=pool_v, pool_table=pool_table)
+                        slopes=slopes, softcap=softcap, sinks=sinks, pool=pool, pool_k=pool_k, pool_v=pool_v, pool_table=pool_table,
+                        chunk=chunk)

@@ -390,3 +390,191 @@ class PooledWindowAttention(Mixer):
         inner = self.rt.empty((h.shape[0], self.inner_size))
         self.inner(pre, step, cache, inner, 1.0, write_cache)
         return self.o.forward(inner, out_dtype=torch.float32)
+
+
+def _attention_plan_key(rt: Runtime, heads: int, kv_heads: int, dim: int, vdim: int) -> Optional[Hashable]:
+    """The tile lists of the tensor-core kernels, as GQAttention's: they depend on the group size alone."""
+    g = heads // kv_heads
+    return ("attention tiles", g) if rt.fast_kernels and g <= TILE_ROWS and vdim == dim else None
+
+
+def _attention_plan(batch: BatchShape, heads: int, kv_heads: int) -> StepPlan:
+    g = heads // kv_heads
+    if batch.max_q_len == 1:
+        key = (g, len(batch.q_lens))
+        hit = GQAttention._decode_plans.get(key)
+        if hit is None:
+            hit = GQAttention._decode_plans[key] = plan_tiles(batch, g)
+        return hit
+    return plan_tiles(batch, g)
+
+
+class TiedChunkAttention(Mixer):
+    """Softmax attention whose values are its keys as projected, inside chunks of positions, with a sink of score 0:
+
+        q = rotate(rmsnorm_head(W_q x) * n_q)      k = rotate(rmsnorm_head(c) * n_k)      v = c      with c = W_k x
+            (per-head RMS norms with one weight [dim] for all heads; the first rot_dims entries of a head are rotated)
+        the query at position i sees the keys j <= i with floor(j / chunk) = floor(i / chunk), chunks counted from the
+            sequence's start (chunk 0: every j <= i)
+        out_h = sum_j exp(s_j) v_j / (sink + sum_j exp(s_j)),   s_j = (q . k_j) * scale,   sink = 1 (a term of score 0
+            without a value) or 0
+
+    There is no value projection: the cache holds the normed, rotated keys and, as values, the same projection before
+    norm and rotation.  A chunk's keys never reach back further than `chunk` tokens, so the pages are a window group of
+    that length and go back as the chunk passes.  W_q | W_k are one product with 32-bit output.
+
+    Beside forward(), the mixer offers its steps apart (in_names / in_sizes, inner, `o`)."""
+    recordable = True
+
+    def __init__(self, rt: Runtime, prefix: str, width: int, heads: int, kv_heads: int, dim: int, scale: float,
+                 position_encoding: Optional[PositionEncoding], chunk: int, eps: float, sink: bool = True,
+                 out_dtype: Optional[torch.dtype] = None):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
+        if position_encoding is not None and position_encoding.rotary_table() is None:
+            raise ValueError("this attention rotates by a table of frequencies (rotary_table)")
+        self.rt, self.prefix, self.width = rt, prefix, width
+        self.heads, self.kv_heads, self.dim = heads, kv_heads, dim
+        self.scale, self.chunk, self.eps, self.sink = float(scale), int(chunk), float(eps), bool(sink)
+        self.position_encoding, self.out_dtype = position_encoding, out_dtype
+        self.q_size, self.k_size, self.inner_size = heads * dim, kv_heads * dim, heads * dim
+        self.proj = Linear(rt, self.in_names(), width, self.in_sizes())
+        self.o = Linear(rt, f"{prefix}.o", self.inner_size, width)
+        self.q_norm_w = self.k_norm_w = self.sinks = None
+
+    def in_names(self) -> list[str]:
+        return [f"{self.prefix}.q", f"{self.prefix}.k"]
+
+    def in_sizes(self) -> list[int]:
+        return [self.q_size, self.k_size]
+
+    def children(self) -> list[Part]:
+        return [self.proj, self.o]
+
+    def param_specs(self) -> list[ParamSpec]:
+        return [ParamSpec(f"{self.prefix}.q.norm", (self.dim,), "norm"), ParamSpec(f"{self.prefix}.k.norm", (self.dim,), "norm")]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        self.q_norm_w = get(f"{self.prefix}.q.norm").to(torch.float32).contiguous()
+        self.k_norm_w = get(f"{self.prefix}.k.norm").to(torch.float32).contiguous()
+        self.sinks = torch.zeros(self.heads, dtype=torch.float32, device=self.rt.device) if self.sink else None
+
+    def plan_key(self) -> Optional[Hashable]:
+        return _attention_plan_key(self.rt, self.heads, self.kv_heads, self.dim, self.dim)
+
+    def plan(self, batch: BatchShape) -> Optional[StepPlan]:
+        return _attention_plan(batch, self.heads, self.kv_heads)
+
+    def cache_request(self) -> KVPages:
+        return KVPages(self.kv_heads, self.dim, self.chunk)
+
+    def inner(self, pre: torch.Tensor, step: StepContext, cache: KVCacheView, out: torch.Tensor, out_scale: float = 1.0,
+              write_cache: bool = True) -> None:
+        """pre: float32 [T, >= sum(in_sizes())], the columns q | k of this mixer; out: [T, inner_size] in the activation type
+        (contiguous) receives the heads."""
+        if out_scale != 1.0 or not out.is_contiguous():
+            raise ops.KernelError("this attention writes unscaled heads into a matrix of their own")
+        rt = self.rt
+        T, H, G, D = pre.shape[0], self.heads, self.kv_heads, self.dim
+        k_in = pre[:, self.q_size:self.q_size + self.k_size]
+        rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
+        inv_freq, rot = rotary if rotary is not None else (None, 0)
+        q = rt.empty((T, H, D))
+        # the keys' projection goes in twice: normed and rotated as keys, and as it is as values
+        ops.rope_kv(pre[:, :self.q_size], k_in, k_in, q, step.positions, H, G if write_cache else 0, D, self.eps, rt.stream,
+                    q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, inv_freq=inv_freq, rot_dim=rot, k_cache=cache.k, v_cache=cache.v,
+                    token_seq=step.token_seq, block_table=step.block_tables[cache.group], page_size=cache.page_size,
+                    rot_scale=getattr(self.position_encoding, "magnitude", 1.0))
+        ops.attention(q, out.view(T, H, D), cache.k, cache.v, step, cache.group, H, G, D, cache.page_size, 0, self.scale, rt.stream,
+                      plan=step.plans.get(self.plan_key()), sinks=self.sinks, chunk=self.chunk)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache: KVCacheView, write_cache: bool = True) -> torch.Tensor:
+        pre = self.proj.forward(h, out_dtype=torch.float32)
+        inner = self.rt.empty((h.shape[0], self.inner_size))
+        self.inner(pre, step, cache, inner, 1.0, write_cache)
+        return self.o.forward(inner, out_dtype=self.out_dtype)
+
+
+class GatedWindowAttention(Mixer):
+    """Softmax attention over a sliding window with biases on q, k and v, rotation (whose sines and cosines may carry a
+    magnitude, as with YaRN) and an elementwise sigmoid gate on the heads:
+
+        q = rotate(W_q x + b_q)      k = rotate(W_k x + b_k)      v = W_v x + b_v
+        the query at position i sees the keys j with 0 <= i - j < window (window 0: every j <= i)
+        out = softmax(q . k * scale) v * sigmoid(W_g x)           (the gate has heads * vdim entries)
+
+    Values may have another size than keys.  W_q | W_k | W_v | W_g are one product with 32-bit output; the biases are
+    added to it in 32-bit.  Beside forward(), the mixer offers its steps apart (in_names / in_sizes, inner, `o`)."""
+    recordable = True
+
+    def __init__(self, rt: Runtime, prefix: str, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                 position_encoding: Optional[PositionEncoding], window: int, out_dtype: Optional[torch.dtype] = None):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
+        if position_encoding is not None and position_encoding.rotary_table() is None:
+            raise ValueError("this attention rotates by a table of frequencies (rotary_table)")
+        self.rt, self.prefix, self.width = rt, prefix, width
+        self.heads, self.kv_heads, self.dim, self.vdim = heads, kv_heads, dim, vdim
+        self.scale, self.window = float(scale), int(window)
+        self.position_encoding, self.out_dtype = position_encoding, out_dtype
+        self.q_size, self.k_size, self.v_size, self.inner_size = heads * dim, kv_heads * dim, kv_heads * vdim, heads * vdim
+        self.proj = Linear(rt, self.in_names(), width, self.in_sizes())
+        self.o = Linear(rt, f"{prefix}.o", self.inner_size, width)
+        self.q_b = self.k_b = self.v_b = None
+
+    def in_names(self) -> list[str]:
+        p = self.prefix
+        return [f"{p}.q", f"{p}.k", f"{p}.v", f"{p}.g"]
+
+    def in_sizes(self) -> list[int]:
+        return [self.q_size, self.k_size, self.v_size, self.inner_size]
+
+    def children(self) -> list[Part]:
+        return [self.proj, self.o]
+
+    def param_specs(self) -> list[ParamSpec]:
+        p = self.prefix
+        return [ParamSpec(f"{p}.q.b", (self.q_size,), "linear"), ParamSpec(f"{p}.k.b", (self.k_size,), "linear"),
+                ParamSpec(f"{p}.v.b", (self.v_size,), "linear")]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        f = lambda n: get(f"{self.prefix}.{n}").to(torch.float32).contiguous()
+        self.q_b, self.k_b, self.v_b = f("q.b"), f("k.b"), f("v.b")
+
+    def plan_key(self) -> Optional[Hashable]:
+        return _attention_plan_key(self.rt, self.heads, self.kv_heads, self.dim, self.vdim)
+
+    def plan(self, batch: BatchShape) -> Optional[StepPlan]:
+        return _attention_plan(batch, self.heads, self.kv_heads)
+
+    def cache_request(self) -> KVPages:
+        return KVPages(self.kv_heads, self.dim, self.window, v_head_dim=self.vdim if self.vdim != self.dim else 0)
+
+    def inner(self, pre: torch.Tensor, step: StepContext, cache: KVCacheView, out: torch.Tensor, out_scale: float = 1.0,
+              write_cache: bool = True) -> None:
+        """pre: float32 [T, >= sum(in_sizes())], the columns q | k | v | g of this mixer, of which q, k, v are changed in
+        place; out: [T, inner_size] in the activation type (may be a column range of a wider matrix) receives the gated
+        heads times out_scale."""
+        rt = self.rt
+        T, H, G, D, V = pre.shape[0], self.heads, self.kv_heads, self.dim, self.vdim
+        c1, c2, c3 = self.q_size, self.q_size + self.k_size, self.q_size + self.k_size + self.v_size
+        ops.bias_rmsnorm_cols(pre, [(0, self.q_size, self.q_b, None), (c1, self.k_size, self.k_b, None), (c2, self.v_size, self.v_b, None)],
+                              0.0, rt.stream)
+        rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
+        inv_freq, rot = rotary if rotary is not None else (None, 0)
+        q = rt.empty((T, H, D))
+        ops.rope_kv(pre[:, :c1], pre[:, c1:c2], pre[:, c2:c3], q, step.positions, H, G if write_cache else 0, D, 0.0, rt.stream,
+                    inv_freq=inv_freq, rot_dim=rot, k_cache=cache.k, v_cache=cache.v, token_seq=step.token_seq,
+                    block_table=step.block_tables[cache.group], page_size=cache.page_size, v_dim=V,
+                    rot_scale=getattr(self.position_encoding, "magnitude", 1.0))
+        heads = rt.empty((T, H, V))
+        ops.attention(q, heads, cache.k, cache.v, step, cache.group, H, G, D, cache.page_size, self.window, self.scale, rt.stream,
+                      plan=step.plans.get(self.plan_key()), v_dim=V if V != D else 0)
+        # an elementwise gate is a gate of one number a "head" of one entry
+        ops.head_gate(out, heads.view(T, H * V, 1), pre[:, c3:c3 + H * V], out_scale, rt.stream)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache: KVCacheView, write_cache: bool = True) -> torch.Tensor:
+        pre = self.proj.forward(h, out_dtype=torch.float32)
+        inner = self.rt.empty((h.shape[0], self.inner_size))
+        self.inner(pre, step, cache, inner, 1.0, write_cache)
+        return self.o.forward(inner, out_dtype=self.out_dtype)

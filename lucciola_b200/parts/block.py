@@ -1,4 +1,5 @@
-"""Pre-norm residual block: r += mixer(norm1(r)); r += ffn(norm2(r)) (src/qwen.cc:574-798 of lucciola).
+"""Pre-norm residual block: r += mixer(norm1(r)); r += ffn(norm2(r)) (src/qwen.cc:574-798 of lucciola).  A block may
+have no feed-forward: then it is its first half alone.
 
 The residual stream is float32.  A block hands the output of its feed-forward on as `delta`
 instead of adding it: the next block's first norm adds it in the same pass (one kernel
@@ -22,13 +23,22 @@ class PreNormBlock(Block):
     fuse_norms = "both"
     recordable = True
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm, act_dtype: torch.dtype):
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm, ffn_norm: Optional[Norm],
+                 act_dtype: torch.dtype):
+        if (feed_forward is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
         self.act_dtype = act_dtype
 
     def children(self) -> list[Part]:
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None]
+
+    @property
+    def takes_delta_parts(self) -> bool:
+        """A norm that adds two deltas in the pass in which it norms takes what the model wants added before this block
+        (the output of the block before and, say, the embedding's output once more) as a tuple."""
+        return hasattr(self.mixer_norm, "add_forward_pair")
 
     def entry_sink(self, residual: torch.Tensor, num_tokens: int, write_cache: bool) -> Optional[NormSink]:
         """The block before may add its output to the residual stream itself and hand it over without the first norm's
@@ -41,7 +51,14 @@ class PreNormBlock(Block):
                 next_sink: Optional[NormSink] = None):
         # Between two products, the add into the residual stream and the norm either run as a kernel of their own, or,
         # where the product before and the product after can, inside those two (NormSink, RowScaled).
-        h = delta if isinstance(delta, RowScaled) else self.mixer_norm.add_forward(residual, delta, self.act_dtype)
+        if isinstance(delta, RowScaled):
+            h = delta
+        elif isinstance(delta, tuple):
+            h, _ = self.mixer_norm.add_forward_pair(residual, delta, None, self.act_dtype)
+        else:
+            h = self.mixer_norm.add_forward(residual, delta, self.act_dtype)
+        if self.feed_forward is None:
+            return residual, self.mixer.forward(h, step, cache, write_cache)
         sink = None
         if self.fuse_norms in ("both", "middle") and self.mixer.accepts_sink and self.feed_forward.row_scaled_ok(step.num_tokens):
             sink = self.ffn_norm.as_sink(residual)

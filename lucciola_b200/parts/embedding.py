@@ -15,11 +15,15 @@ class TokenEmbedding(Part):
     With `positions_name` the model has a table of learned position vectors [max_positions, hidden], and
     residual[t, :] += positions[p_t, :] (unscaled, added in 32-bit); forward() then takes the tokens' positions.
     With `sinusoid_base` b a sinusoidal vector is added instead, for positions without a limit: entry 2i is
-    sin(p * b^(-2i / hidden)), entry 2i + 1 the cosine of the same angle; the frequencies are made once in 64-bit."""
+    sin(p * b^(-2i / hidden)), entry 2i + 1 the cosine of the same angle; the frequencies are made once in 64-bit.
+    `scale` multiplies the table's row (in 32-bit); an output head tied to the table reads it unscaled."""
     recordable = True
 
     def __init__(self, rt: Runtime, name: str, vocab_size: int, hidden_size: int, positions_name: str | None = None,
-                 max_positions: int = 0, sinusoid_base: float | None = None):
+                 max_positions: int = 0, sinusoid_base: float | None = None, scale: float = 1.0):
+        self.scale = float(scale)
+        if sinusoid_base is not None and self.scale != 1.0:
+            raise ValueError("sinusoidal positions come with an unscaled embedding")
         self.rt, self.name, self.vocab_size, self.hidden_size = rt, name, vocab_size, hidden_size
         self.positions_name, self.max_positions = positions_name, max_positions
         if positions_name is not None and max_positions <= 0:
@@ -49,16 +53,20 @@ class TokenEmbedding(Part):
             i = torch.arange((self.hidden_size + 1) // 2, dtype=torch.float64)
             self.sin_freq = (self.sinusoid_base ** (-2.0 * i / self.hidden_size)).to(self.weight.device).contiguous()
 
-    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor | None = None, copy: torch.Tensor | None = None) -> torch.Tensor:
+        """`copy` (float32 [T, hidden]) receives the output a second time, for a model that adds it to the stream again."""
         out = self.rt.empty((token_ids.shape[0], self.hidden_size), torch.float32)
+        if copy is not None and self.sinusoid_base is not None:
+            raise ValueError("no second copy of an embedding with sinusoidal positions")
         if self.uses_positions and positions is None:
             raise ValueError("this embedding adds position vectors and needs the tokens' positions")
         if self.sinusoid_base is not None:
             ops.embedding(out, token_ids, self.weight, self.rt.stream, positions=positions, sin_freq=self.sin_freq)
         elif self.positions_name is not None:
-            ops.embedding(out, token_ids, self.weight, self.rt.stream, pos_table=self.position_table, positions=positions)
+            ops.embedding(out, token_ids, self.weight, self.rt.stream, pos_table=self.position_table, positions=positions,
+                          scale=self.scale, copy=copy)
         else:
-            ops.embedding(out, token_ids, self.weight, self.rt.stream)
+            ops.embedding(out, token_ids, self.weight, self.rt.stream, scale=self.scale, copy=copy)
         return out
 
 

@@ -81,7 +81,7 @@ class SwiGLUFeedForward(GatedFeedForward):
 
 
 class DenseFeedForward(FeedForward):
-    """A feed-forward without a gate: down( act(up(h)) ).  `act` is one of ops.PLAIN_ACTS; xIELU,
+    """A feed-forward without a gate: down( act(up(h)) ).  `act` is one of ops.PLAIN_ACTS ("relu2" is relu(z)^2); xIELU,
 
         z > 0: softplus(p) z^2 + z / 2        z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2,
 

@@ -30,13 +30,19 @@ class SideBySideMixer(Mixer):
         self.n_left = sum(left.in_sizes())
         self.proj = Linear(rt, left.in_names() + right.in_names(), width, left.in_sizes() + right.in_sizes())
         self.o = Linear(rt, [left.o.names[0], right.o.names[0]], [left.inner_size, right.inner_size], width)
+        # a mixer may keep several things (a tuple): the pair asks for the two laid end to end and hands each its share
+        self._left_tuple, self._right_tuple = isinstance(left.cache_request(), tuple), isinstance(right.cache_request(), tuple)
+        self._n_left_caches = len(left.cache_request()) if self._left_tuple else 1
 
     @property
     def recordable(self) -> bool:
         return bool(self.left.recordable and self.right.recordable)
 
     def children(self) -> list[Part]:
-        return [self.proj, self.o]
+        # the mixers' own children (a convolution, say) but for their input and output products, which this part's replace
+        own = [c for m in (self.left, self.right) for c in m.children()
+               if c is not m.o and not (isinstance(c, Linear) and c.names == list(m.in_names()))]
+        return [self.proj, self.o, *own]
 
     def param_specs(self) -> list[ParamSpec]:
         # the two mixers' own tensors (norm weights and the like); their products' tensors are this part's
@@ -47,7 +53,8 @@ class SideBySideMixer(Mixer):
         self.right.bind(get)
 
     def cache_request(self) -> tuple:
-        return (self.left.cache_request(), self.right.cache_request())
+        a, b = self.left.cache_request(), self.right.cache_request()
+        return (a if self._left_tuple else (a,)) + (b if self._right_tuple else (b,))
 
     def plan_key(self) -> Optional[Hashable]:
         a, b = self.left.plan_key(), self.right.plan_key()
@@ -59,7 +66,9 @@ class SideBySideMixer(Mixer):
         return (self.left if self.left.plan_key() is not None else self.right).plan(batch)
 
     def forward(self, h: torch.Tensor, step: StepContext, cache, write_cache: bool = True) -> torch.Tensor:
-        left_cache, right_cache = cache
+        left_cache, right_cache = cache[:self._n_left_caches], cache[self._n_left_caches:]
+        left_cache = left_cache if self._left_tuple else left_cache[0]
+        right_cache = right_cache if self._right_tuple else right_cache[0]
         pre = self.proj.forward(h, out_dtype=torch.float32)
         kl = self.left.inner_size
         inner = self.rt.empty((h.shape[0], kl + self.right.inner_size))
