@@ -33,6 +33,9 @@ bias beside decay linear attention; gelu feed-forwards and routed experts in tur
 `--design nelovik` does the same for the Nelovik design (parallel blocks with a norm for each sublayer; layers of the gated delta
 rule and, every fourth, windowed attention with pooled blocks, capped scores and sinks beside a Mamba-2 state space; an xIELU
 feed-forward), beside Bonolorn and Qwen3 at equal sizes.
+`--design venitar` does the same for the Venitar design (pre-norm blocks of which the first two run twice; window attention with
+YaRN rotation and a sigmoid gate beside a gated delta rule with a decay for every key channel, retention, and attention in chunks
+whose values are its keys, with a sink; a relu-squared feed-forward), beside Nelovik and Qwen3 at equal sizes.
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures 6650 GB/s and 1590 TFLOP/s.  The timed work reads far more than the 126 MB of L2
@@ -440,7 +443,8 @@ DESIGN_SIZES = {
 
 
 # the models a --design run measures: the design and the nearest ones beside it
-DESIGN_BESIDE = {"riruzen": ("riruzen", "qwen3"), "bonolorn": ("riruzen", "qwen3", "bonolorn"), "nelovik": ("nelovik", "bonolorn", "qwen3")}
+DESIGN_BESIDE = {"riruzen": ("riruzen", "qwen3"), "bonolorn": ("riruzen", "qwen3", "bonolorn"), "nelovik": ("nelovik", "bonolorn", "qwen3"),
+                 "venitar": ("venitar", "nelovik", "qwen3")}
 
 
 def design_configs(size: dict, layers: int, positions: int) -> dict:
@@ -475,7 +479,64 @@ def design_configs(size: dict, layers: int, positions: int) -> dict:
     order = [delta("delta", max(H // 2, 1)), delta("delta_2", H), delta("delta", max(H // 2, 1)), pair]
     nelovik = {"architecture": "Nelovik", "vocab": size["vocab"], "width": W, "norm": {"eps": 1e-6},
                "layers": [order[i % 4] for i in range(layers)]}
-    return {"riruzen": riruzen, "qwen3": qwen3, "bonolorn": bonolorn, "nelovik": nelovik}
+    # Venitar: `layers` runs of layers, of which the first two run twice (so two fewer distinct layers): in turn a pair of window
+    # attention (half the heads, a quarter as many kv heads, window 1024, YaRN) beside the delta rule with channel decays (half the
+    # heads, a 128 x 128 state, ranks 64), retention (all heads, a 128 x 128 state; no feed-forward), attention in chunks of 1024
+    # whose values are its keys, and retention with a feed-forward
+    ffd = {"kind": "dense", "ff": size["ff"]}
+    vpair = {"type": "parallel", "mlp": ffd, "mixer": {
+        "left": {"heads": H // 2, "kv_heads": max(H // 8, 1), "dim": D, "vdim": D, "scale": D ** -0.5,
+                 "rot": {"dims": D // 2, "base": 1e6, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}, "mask": {"size": 1024}},
+        "right": {"heads": H // 2, "kv_heads": max(H // 4, 1), "dim": D, "vdim": D, "conv": 4, "decay_rank": 64, "gate_rank": 64},
+        "left_scale": 0.8, "right_scale": 0.9}}
+    def ret(ff):
+        return {"type": "retention", "mlp": ff, "mixer": {"heads": H, "dim": D, "vdim": D, "rot": {"dims": D, "base": 1e6},
+                                                          "decay": [1.0 - 2.0 ** -(3 + 8 * h / max(H - 1, 1)) for h in range(H)]}}
+    vatt = {"type": "attention", "mlp": ffd, "mixer": {"heads": H, "kv_heads": max(H // 4, 1), "dim": D, "vdim": D, "scale": D ** -0.5,
+                                                       "rot": {"dims": D // 2, "base": 1e4}, "mask": {"size": 1024}}}
+    vorder = [vpair, ret(None), vatt, ret(ffd)]
+    looped = layers >= 4
+    venitar = {"architecture": "Venitar", "vocab": size["vocab"], "width": W, "embedding": {"scale": 0.5}, "norm": {"eps": 1e-6},
+               "loop": {"start": 0, "stop": 2 if looped else 0, "times": 2 if looped else 1},
+               "layers": [vorder[i % 4] for i in range(layers - 2 if looped else layers)]}
+    return {"riruzen": riruzen, "qwen3": qwen3, "bonolorn": bonolorn, "nelovik": nelovik, "venitar": venitar}
+
+
+def venitar_costs(cfg: dict) -> dict:
+    """The same for a Venitar configuration, run by run (a layer that runs twice is read twice: its weights are far more than the
+    L2 holds).  What a decoded token reads of a sequence differs by layer (a window's keys, the keys of the chunk so far), so the
+    cache's bytes are a function of the context (`cache_bytes`); states and the convolutions' last inputs are read and written."""
+    W = cfg["width"]
+    loop = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    runs = list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] + list(range(loop["stop"], len(cfg["layers"])))
+    weights = request_bytes = 0
+    attn, cache = [], []
+    for i in runs:
+        l = cfg["layers"][i]
+        m = l["mixer"]
+        if l["type"] == "parallel":
+            a, r = m["left"], m["right"]
+            qk, inner = r["kv_heads"] * r["dim"], r["heads"] * r["vdim"]
+            weights += (a["heads"] * a["dim"] + a["kv_heads"] * (a["dim"] + a["vdim"]) + a["heads"] * a["vdim"]) * W + W * a["heads"] * a["vdim"]
+            weights += (2 * qk + inner + r["heads"] + r["decay_rank"] + r["gate_rank"]) * W + r["heads"] * r["dim"] * r["decay_rank"] \
+                + inner * r["gate_rank"] + W * inner
+            request_bytes += 2 * 4 * r["heads"] * r["dim"] * r["vdim"] + 2 * 4 * (r["conv"] - 1) * (2 * qk + inner)
+            cache.append(lambda c, a=a: 2 * a["kv_heads"] * (a["dim"] + a["vdim"]) * min(c, a["mask"]["size"]))
+            attn.append(lambda T, a=a, r=r: a["heads"] * 2.0 * (a["dim"] + a["vdim"]) * sum(min(t + 1, a["mask"]["size"]) for t in range(T))
+                        + 10.0 * T * r["heads"] * r["dim"] * r["vdim"])
+        elif l["type"] == "retention":
+            weights += (2 * m["heads"] * m["dim"] + 2 * m["heads"] * m["vdim"]) * W + W * m["heads"] * m["vdim"]
+            request_bytes += 2 * 4 * m["heads"] * m["dim"] * m["vdim"]
+            attn.append(lambda T, m=m: 6.0 * T * m["heads"] * m["dim"] * m["vdim"])
+        else:
+            weights += (m["heads"] + m["kv_heads"]) * m["dim"] * W + W * m["heads"] * m["dim"]
+            cache.append(lambda c, m=m: 2 * m["kv_heads"] * 2 * m["dim"] * (c % m["mask"]["size"] + 1))
+            attn.append(lambda T, m=m: m["heads"] * 4.0 * m["dim"] * sum(t % m["mask"]["size"] + 1 for t in range(T)))
+        if l["mlp"]:
+            weights += 2 * l["mlp"]["ff"] * W
+    return {"weight_bytes": 2 * (weights + cfg["vocab"] * W), "token_bytes": 0, "request_bytes": request_bytes,
+            "flops_per_token": 2.0 * weights, "attn_flops": lambda T: sum(f(T) for f in attn),
+            "cache_bytes": lambda c: sum(f(int(c)) for f in cache)}
 
 
 def nelovik_costs(cfg: dict) -> dict:
@@ -545,6 +606,8 @@ def design_costs(name: str, cfg: dict) -> dict:
         return bonolorn_costs(cfg)
     if name == "nelovik":
         return nelovik_costs(cfg)
+    if name == "venitar":
+        return venitar_costs(cfg)
     if name == "qwen3":
         L = cfg["num_hidden_layers"]
         per_layer, weight_bytes, kv = model_bytes_and_flops(cfg, L)
@@ -659,6 +722,8 @@ def run_design(args) -> int:
                 if cost.get("pool"):                                                            # one entry a whole block behind it
                     seen += max(0.0, mean_ctx - cost["window"]) // cost["pool"]
                 step_bytes = cost["weight_bytes"] + B * (seen * cost["token_bytes"] + cost["request_bytes"])
+                if cost.get("cache_bytes"):                                                     # layers that see different parts of the context
+                    step_bytes += B * cost["cache_bytes"](mean_ctx)
                 step_bytes += sum(2 * one * min(E, B * top) for one, E, top in cost.get("expert_layers", ()))
                 out[f"decode_b{B}"] = {"context": int(mean_ctx), "ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1),
                                        "launches_per_step": (runner.kernel_launches() - launches0) // steps,
@@ -704,12 +769,12 @@ def main() -> int:
     ap.add_argument("--portion", type=int, default=512, help="tokens of the portion of a --profile mixed step")
     ap.add_argument("--time-kernel", choices=["attention_key_ranges"], default=None,
                     help="time one kernel alone over a grid of sizes, print a line of JSON a case, and exit")
-    ap.add_argument("--design", choices=["riruzen", "bonolorn", "nelovik"], default=None,
+    ap.add_argument("--design", choices=["riruzen", "bonolorn", "nelovik", "venitar"], default=None,
                     help="instead of the default workload: prefill and decode of this design beside the Qwen3 decoder at equal "
                          "sizes (--design-sizes; --layers, default 8; --prefill-tokens; --context up to 2048; --profile decode|prefill "
                          "with --batch runs one step between cudaProfilerStart/Stop)")
     ap.add_argument("--design-sizes", default="w2048,w4096", help="which of %s" % ", ".join(sorted(DESIGN_SIZES)))
-    ap.add_argument("--design-models", default="", help="which of riruzen, qwen3, bonolorn, nelovik (empty: the design and those beside it)")
+    ap.add_argument("--design-models", default="", help="which of riruzen, qwen3, bonolorn, nelovik, venitar (empty: the design and those beside it)")
     args = ap.parse_args()
     if args.time_kernel == "attention_key_ranges":
         return time_attention_key_ranges()
