@@ -666,6 +666,10 @@ def run_design(args) -> int:
             pages = 64 * (-(-(ctx + K + Wm + 8) // page)) + -(-T // page) + 64
             options = EngineOptions(dtype="bfloat16", block_size=page, max_blocks=pages, max_num_seqs=66, max_tokens_per_step=T + 64,
                                     use_cuda_graph=not (args.no_graph or args.profile))
+            if args.design == "venitar":
+                # designs whose positions have no limit of their own get the run's: block tables as wide as the run needs
+                options = EngineOptions(dtype="bfloat16", block_size=page, max_blocks=pages, max_num_seqs=66, max_tokens_per_step=T + 64,
+                                        use_cuda_graph=not (args.no_graph or args.profile), max_model_len=max(ctx, T) + K + Wm + 64)
             runner = build_runner_random(cfg, 0, options, std=0.02, num_pages=pages)
             ev = lambda: torch.cuda.Event(enable_timing=True)
             out = {"design": mname, "size": sname, "layers": layers, "dtype": "bf16", "data": "synthetic: random token ids, random weights"}

@@ -4,7 +4,8 @@
 //
 //   delta rule    g = exp(-exp(A_h) softplus(a_t + dt_h))     w = sigmoid(b_t)
 //                 S <- g S;   u = w (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
-//                 (rows_decay: g is a vector, one decay for every row r of the state, from a_t[h, r] and dt[h, r]; S <- diag(g) S)
+//                 (rows_decay: g is a vector, one decay for every row r of the state, S <- diag(g) S; `a` holds the decays, made by
+//                  lb_channel_decay from a_t[h, r] and dt[h, r])
 //   state space   w = softplus(a_t + dt_h)     g = exp(-exp(A_h) w)
 //                 S <- g S + k_t (w v_t)^T;    o_t = S^T q_t + D_h v_t          (k = B, q = C, v = x)
 //
@@ -62,8 +63,9 @@ __host__ __device__ constexpr int sr_smem_floats(int rpl, int sub, int tokens, b
   return 4 * tokens * row + 2 * tokens * cols + 6 * (tokens < 4 ? 4 : tokens) + tile + (rows_decay ? 2 * tokens * row : 0);
 }
 
-// VG: the decay is a vector, one number for every row of the state (key channel) and token: `a` holds heads * dim
-// numbers a token and dt_bias heads * dim, g[r] = exp(-exp(A_h) softplus(a[h, r] + dt[h, r])), and S <- diag(g) S.
+// VG: the decay is a vector, one number for every row of the state (key channel) and token, S <- diag(g) S.  `a` then
+// holds the decays themselves, heads * dim numbers a token, as lb_channel_decay leaves them: formed once for all the
+// CTAs that share a head, and off the path from one token to the next.
 template <bool DELTA, int RPL, int SUB, int TOK, bool VG = false>
 __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecurrenceParams p) {
   constexpr int T = TOK, COLS = SR_THREADS / SUB, ROW = (RPL + 4) * SUB, DP = RPL * SUB;
@@ -78,14 +80,14 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
   float* w_s = g_s + TS;                          // [TS] write strength
   float* o_s = w_s + TS;                          // [T][COLS][SUB] partial read-outs; the state's tile [DP][COLS] at both ends
   constexpr int TILE = T * SR_THREADS > DP * COLS ? T * SR_THREADS : DP * COLS;
-  float* gv_s = o_s + TILE;                       // VG: [2][T][ROW], laid out as k_s: first the step sizes as fetched, then the decays
+  float* gv_s = o_s + TILE;                       // VG: [2][T][ROW], laid out as k_s: the decays of the state's rows
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = tid % SUB, col_local = tid / SUB;
   const int h = blockIdx.y, seq = blockIdx.z;
   const int col0 = blockIdx.x * COLS;
   const int grp = h / (p.heads / p.groups);
-  const float A = expf(p.A_log[h]), dtb = VG ? 0.f : p.dt_bias[h];
+  const float A = VG ? 0.f : expf(p.A_log[h]), dtb = VG ? 0.f : p.dt_bias[h];
   const float Dh = p.D ? p.D[h] : 0.f;
   if (p.dim < DP || col0 + COLS > p.vdim) {        // rows past dim and columns past vdim stay zero; nothing else of the buffers is read unwritten
     for (int i = tid; i < 4 * T * ROW + 2 * T * COLS; i += SR_THREADS) sr_smem[i] = 0.f;
@@ -178,10 +180,6 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
     const float* vb = v_s + buf * T * COLS;
     float* gb = gv_s + buf * T * ROW;
     if (VG) {
-      for (int i = tid; i < nt * p.dim; i += SR_THREADS) {
-        const int tt = i / p.dim, r = i % p.dim, at = tt * ROW + r + 4 * (r / RPL);
-        gb[at] = expf(-A * softplus_f(gb[at] + p.dt_bias[(size_t)h * p.dim + r]));
-      }
       if (tid < nt) w_s[tid] = 1.f / (1.f + expf(-b_s[buf * TS + tid]));
     } else if (tid < nt) {
       const float sp = softplus_f(a_s[buf * TS + tid] + dtb);
@@ -265,6 +263,19 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
       const int r = i / COLS, c = i % COLS, col = col0 + c;
       if (r < p.dim && col < p.vdim) S[(size_t)r * p.vdim + col] = o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS];
     }
+  }
+}
+
+// Decays for every key channel, in place: a[t, h * dim + r] <- exp(-exp(A_log[h]) * softplus(a[t, h * dim + r] + dt_bias[h * dim + r])).
+__global__ void channel_decay_kernel(float* __restrict__ a, long long a_ld, const float* __restrict__ A_log,
+                                     const float* __restrict__ dt_bias, int n, int dim, long long total) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / n;
+    const int c = (int)(idx - t * n);
+    float* x = a + t * a_ld + c;
+    *x = expf(-expf(A_log[c / dim]) * softplus_f(*x + dt_bias[c]));
   }
 }
 
@@ -376,6 +387,17 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
 #undef LB_SR1
 #undef LB_SR
   LB_CHECK_LAUNCH("state_recurrence");
+  return 0;
+}
+
+LB_EXPORT int lb_channel_decay(float* a, long long a_ld, const float* A_log, const float* dt_bias, int num_rows, int heads, int dim,
+                               cudaStream_t stream) {
+  LB_CHECK_ARG(a && A_log && dt_bias && num_rows >= 0 && heads > 0 && dim > 0 && a_ld >= (long long)heads * dim, "channel_decay: bad arguments");
+  if (num_rows == 0) return 0;
+  const long long total = (long long)num_rows * heads * dim;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  lb::launch(lb::channel_decay_kernel, dim3(blocks), dim3(256), 0, stream, a, a_ld, A_log, dt_bias, heads * dim, dim, total);
+  LB_CHECK_LAUNCH("channel_decay");
   return 0;
 }
 

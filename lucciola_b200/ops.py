@@ -80,6 +80,7 @@ _SIGNATURES = {
     "lb_state_recurrence": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                             c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p],
+    "lb_channel_decay": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lb_gated_group_norm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_longlong, c_void_p],
     "lb_bias_rmsnorm_cols": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
@@ -422,7 +423,9 @@ def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch
     delta=True the gated delta rule (b: beta's input), else the state space of Mamba-2 (k = B, q = C, v = x, a = dt's
     input, D optional).  q, k [T, groups * dim], v [T, heads * vdim], a, b [T, heads]: float32 rows, column ranges allowed;
     state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32.
-    `rows_decay` (delta rule only): a decay for every row of the state; a is then [T, heads * dim] and dt_bias [heads * dim]."""
+    `rows_decay` (delta rule only): a decay for every row of the state; a is then [T, heads * dim] and dt_bias [heads * dim], and
+    a is overwritten with the decays (one pass over it before the recurrence, so that the CTAs that share a head do not each
+    form them again on the path from token to token)."""
     for t, w in ((q, "q"), (k, "k"), (v, "v"), (a, "a")) + (((b, "b"),) if b is not None else ()):
         _rows32(t, w)
     _rows32(out, "recurrence output")
@@ -434,6 +437,8 @@ def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch
             or tuple(a.shape) != (T, heads * dim if rows_decay else heads) or dt_bias.numel() != (heads * dim if rows_decay else heads)
             or tuple(out.shape) != (T, heads * vdim) or tuple(state.shape[1:]) != (heads, dim, vdim)):
         raise KernelError("the recurrence's operands do not fit its head counts and sizes")
+    if rows_decay:
+        _call("lb_channel_decay", a.data_ptr(), a.stride(0), A_log.data_ptr(), dt_bias.data_ptr(), T, heads, dim, stream)
     _call("lb_state_recurrence", 1 if delta else 0, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
           a.data_ptr(), a.stride(0), _ptr(b), b.stride(0) if b is not None else 0, A_log.data_ptr(), dt_bias.data_ptr(), _ptr(D),
           state.data_ptr(), out.data_ptr(), out.stride(0), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs,
