@@ -15,7 +15,7 @@
 // be column ranges of wider matrices; a, b are one number a head and token.
 //
 // A CTA of 128 threads takes (COLS value columns, a head, a sequence) and walks the sequence's tokens of this step in
-// order.  A column of the state belongs to SUB neighbouring lanes (4 for up to 64 state rows, else 8; COLS = 128 / SUB),
+// order.  A column of the state belongs to SUB neighbouring lanes (4, 8 or 16 by the state's rows; COLS = 128 / SUB),
 // each of which holds RPL consecutive rows in registers and adds its partial dot products to its neighbours' by
 // shuffles; the columns never talk to one another.  The tokens' q, k, v and the two numbers a head are fetched 16
 // tokens at a time by cp.async into one of two buffers, the chunk after the one at work, so the walk never waits for
@@ -69,6 +69,7 @@ __host__ __device__ constexpr int sr_smem_floats(int rpl, int sub, int tokens, b
 template <bool DELTA, int RPL, int SUB, int TOK, bool VG = false>
 __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecurrenceParams p) {
   constexpr int T = TOK, COLS = SR_THREADS / SUB, ROW = (RPL + 4) * SUB, DP = RPL * SUB;
+  constexpr int TURN = 32 / SUB < 4 ? 4 : 32 / SUB;   // columns by which a lane's rows are turned in the state's tile: whole 16-byte words
   extern __shared__ __align__(16) float sr_smem[];
   float* q_s = sr_smem;                           // [2][T][ROW]: row r of a token at r + 4 * (r / RPL)
   float* k_s = q_s + 2 * T * ROW;
@@ -96,19 +97,19 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
   pdl_wait();
   const int first = p.cu_tokens[seq], n = p.cu_tokens[seq + 1] - first;
   float* S = p.state + ((size_t)p.slots[seq] * p.heads + h) * p.dim * p.vdim;
-  const int shift = ((32 / SUB) * sub) % COLS;     // a lane's column of the state's tile, turned so that a warp's lanes spread over the banks
+  const int shift = (TURN * sub) % COLS;     // a lane's column of the state's tile, turned so that a warp's lanes spread over the banks
 
   // the state: whole lines into the tile, then each lane's rows into registers
   if (p.svec) {                                    // 16-byte words: the turn is a multiple of four columns
     for (int i = tid; i < DP * (COLS / 4); i += SR_THREADS) {
       const int r = i / (COLS / 4), c = (i % (COLS / 4)) * 4, col = col0 + c;
       const float4 x = (r < p.dim && col < p.vdim) ? *reinterpret_cast<const float4*>(S + (size_t)r * p.vdim + col) : make_float4(0.f, 0.f, 0.f, 0.f);
-      *reinterpret_cast<float4*>(o_s + r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS) = x;
+      *reinterpret_cast<float4*>(o_s + r * COLS + (c + TURN * (r / RPL)) % COLS) = x;
     }
   } else {
     for (int i = tid; i < DP * COLS; i += SR_THREADS) {
       const int r = i / COLS, c = i % COLS, col = col0 + c;
-      o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS] = (r < p.dim && col < p.vdim) ? S[(size_t)r * p.vdim + col] : 0.f;
+      o_s[r * COLS + (c + TURN * (r / RPL)) % COLS] = (r < p.dim && col < p.vdim) ? S[(size_t)r * p.vdim + col] : 0.f;
     }
   }
   __syncthreads();
@@ -243,7 +244,8 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
       const int tt = i / COLS, cc = i % COLS, col = col0 + cc;
       const float* part = o_s + tt * SR_THREADS + cc * SUB;
       float o = (part[0] + part[1]) + (part[2] + part[3]);
-      if (SUB == 8) o += (part[4] + part[5]) + (part[6] + part[7]);
+      if (SUB >= 8) o += (part[4] + part[5]) + (part[6] + part[7]);
+      if (SUB == 16) o += ((part[8] + part[9]) + (part[10] + part[11])) + ((part[12] + part[13]) + (part[14] + part[15]));
       if (col < p.vdim) p.out[(size_t)(first + t0 + tt) * p.out_ld + (size_t)h * p.vdim + col] = o + Dh * vb[tt * COLS + cc];
     }
   }
@@ -256,12 +258,12 @@ __global__ void __launch_bounds__(SR_THREADS) state_recurrence_kernel(StateRecur
     for (int i = tid; i < DP * (COLS / 4); i += SR_THREADS) {
       const int r = i / (COLS / 4), c = (i % (COLS / 4)) * 4, col = col0 + c;
       if (r < p.dim && col < p.vdim)
-        *reinterpret_cast<float4*>(S + (size_t)r * p.vdim + col) = *reinterpret_cast<const float4*>(o_s + r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS);
+        *reinterpret_cast<float4*>(S + (size_t)r * p.vdim + col) = *reinterpret_cast<const float4*>(o_s + r * COLS + (c + TURN * (r / RPL)) % COLS);
     }
   } else {
     for (int i = tid; i < DP * COLS; i += SR_THREADS) {
       const int r = i / COLS, c = i % COLS, col = col0 + c;
-      if (r < p.dim && col < p.vdim) S[(size_t)r * p.vdim + col] = o_s[r * COLS + (c + (32 / SUB) * (r / RPL)) % COLS];
+      if (r < p.dim && col < p.vdim) S[(size_t)r * p.vdim + col] = o_s[r * COLS + (c + TURN * (r / RPL)) % COLS];
     }
   }
 }
@@ -336,7 +338,7 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
                                   const float* A_log, const float* dt_bias, const float* D, float* state, float* out,
                                   long long out_ld, const int* cu_tokens, const int* slots, int num_seqs, int heads, int groups,
                                   int dim, int vdim, int unit_norm, float q_scale, float unit_eps, int single_tokens, int rows_decay,
-                                  cudaStream_t stream) {
+                                  int wide_lanes, cudaStream_t stream) {
   LB_CHECK_ARG(!rows_decay || delta, "state_recurrence: a decay for every state row comes with the delta rule");
   LB_CHECK_ARG(q && k && v && a && A_log && dt_bias && state && out && cu_tokens && slots && (!delta || b),
                "state_recurrence: null argument");
@@ -380,10 +382,15 @@ LB_EXPORT int lb_state_recurrence(int delta, const float* q, long long q_ld, con
     if (single_tokens) LB_SR1(RPL, SUB, 1);                                                                         \
     else LB_SR1(RPL, SUB, lb::SR_TOKENS);                                                                           \
   } while (0)
+  // Eight rows a lane: the fewer rows a lane walks a token, the shorter the path from one token to the next (the sums
+  // over a column's lanes are a butterfly of log2(SUB) shuffles), which is what a step with few sequences waits for:
+  // a prompt of 2048 tokens with 16 heads of 128 x 128 (128 CTAs) takes a third less time.  A step that fills every SM
+  // several times over (many single tokens; 32 such heads) is bound by the instructions issued, of which sixteen rows a
+  // lane need fewer (10 to 15 % faster); `wide_lanes` asks for that layout.  The two add a column's terms in another order.
   if (dim <= 32) LB_SR(8, 4);
-  else if (dim <= 64) LB_SR(16, 4);
-  else if (dim <= 128) LB_SR(16, 8);
-  else LB_SR(32, 8);
+  else if (dim <= 64) { if (wide_lanes) LB_SR(16, 4); else LB_SR(8, 8); }
+  else if (dim <= 128) { if (wide_lanes) LB_SR(16, 8); else LB_SR(8, 16); }
+  else { if (wide_lanes) LB_SR(32, 8); else LB_SR(16, 16); }
 #undef LB_SR1
 #undef LB_SR
   LB_CHECK_LAUNCH("state_recurrence");

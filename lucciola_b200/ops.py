@@ -79,7 +79,7 @@ _SIGNATURES = {
     "lb_short_conv_state": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lb_state_recurrence": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                             c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
-                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p],
     "lb_channel_decay": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lb_gated_group_norm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_longlong, c_void_p],
@@ -418,14 +418,17 @@ def short_conv_state(state: torch.Tensor, x: torch.Tensor, taps: int, step, stre
 def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None,
                      A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
                      step, heads: int, groups: int, dim: int, vdim: int, stream: int, delta: bool, unit_norm: bool = False,
-                     q_scale: float = 1.0, unit_eps: float = 1e-6, rows_decay: bool = False) -> None:
+                     q_scale: float = 1.0, unit_eps: float = 1e-6, rows_decay: bool = False, by_shape: bool = False) -> None:
     """A recurrence with a decay and a write strength per token over this step's tokens (csrc/state_recurrence.cu):
     delta=True the gated delta rule (b: beta's input), else the state space of Mamba-2 (k = B, q = C, v = x, a = dt's
     input, D optional).  q, k [T, groups * dim], v [T, heads * vdim], a, b [T, heads]: float32 rows, column ranges allowed;
     state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32.
     `rows_decay` (delta rule only): a decay for every row of the state; a is then [T, heads * dim] and dt_bias [heads * dim], and
     a is overwritten with the decays (one pass over it before the recurrence, so that the CTAs that share a head do not each
-    form them again on the path from token to token)."""
+    form them again on the path from token to token).  `by_shape`: the kernel's layout may follow the step's shape (steps of
+    single tokens keep sixteen state rows a lane, which issues fewer instructions; all others eight, which shortens the path
+    from token to token); a column's terms are then added in an order that depends on the step.  Without it one layout
+    serves every step, so a 32-bit result does not depend on how a sequence was cut."""
     for t, w in ((q, "q"), (k, "k"), (v, "v"), (a, "a")) + (((b, "b"),) if b is not None else ()):
         _rows32(t, w)
     _rows32(out, "recurrence output")
@@ -442,7 +445,15 @@ def state_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch
     _call("lb_state_recurrence", 1 if delta else 0, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
           a.data_ptr(), a.stride(0), _ptr(b), b.stride(0) if b is not None else 0, A_log.data_ptr(), dt_bias.data_ptr(), _ptr(D),
           state.data_ptr(), out.data_ptr(), out.stride(0), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs,
-          heads, groups, dim, vdim, 1 if unit_norm else 0, q_scale, unit_eps, 1 if T == step.num_seqs else 0, 1 if rows_decay else 0, stream)
+          heads, groups, dim, vdim, 1 if unit_norm else 0, q_scale, unit_eps, 1 if T == step.num_seqs else 0, 1 if rows_decay else 0,
+          1 if (by_shape and (T == step.num_seqs or _recurrence_fills_sms(step.num_seqs, heads, dim, vdim))) else 0, stream)
+
+
+def _recurrence_fills_sms(num_seqs: int, heads: int, dim: int, vdim: int, sms: int = 148) -> bool:
+    """Whether a step's recurrence has more CTAs than the GPU has SMs already with sixteen state rows a lane (32 value columns
+    a CTA for up to 64 rows, else 16): then the instructions issued bound it, not the path from token to token."""
+    cols = 32 if dim <= 64 else 16
+    return num_seqs * heads * -(-vdim // cols) > sms
 
 
 def gated_group_norm(out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, groups: int, eps: float,

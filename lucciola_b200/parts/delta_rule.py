@@ -150,7 +150,7 @@ class GatedDeltaRule(Mixer):
         o = rt.empty((T, m), torch.float32)
         ops.state_recurrence(qkv[:, :n], qkv[:, n:2 * n], qkv[:, 2 * n:], a, b, self.A_log, self.dt_bias, None, state.state, o, step,
                              H, self.kv_heads, self.dim, self.vdim, rt.stream, delta=True, unit_norm=True, q_scale=self.dim ** -0.5,
-                             unit_eps=UNIT_EPS, rows_decay=bool(self.decay_rank))
+                             unit_eps=UNIT_EPS, rows_decay=bool(self.decay_rank), by_shape=rt.fast_kernels)
         ops.gated_group_norm(out, o, gate, self.norm_w, H, self.eps, rt.stream, gate_first=False, act=self.gate_act, scale=out_scale)
 
     def forward(self, h: torch.Tensor, step: StepContext, cache: tuple, write_cache: bool = True) -> torch.Tensor:

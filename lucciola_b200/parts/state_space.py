@@ -79,7 +79,7 @@ class SelectiveStateSpace(Mixer):
         dt0 = 2 * m + 2 * bc
         ops.state_recurrence(xbc[:, m + bc:], xbc[:, m:m + bc], xbc[:, :m], pre[:, dt0:dt0 + self.heads], None, self.A_log,
                              self.dt_bias, self.D, state.state, y, step, self.heads, self.groups, self.state, self.vdim, rt.stream,
-                             delta=False)
+                             delta=False, by_shape=rt.fast_kernels)
         ops.gated_group_norm(out, y, pre[:, :m], self.norm_w, self.norm_groups, self.eps, rt.stream, gate_first=True, act="silu",
                              scale=out_scale)
 
