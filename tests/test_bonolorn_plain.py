@@ -139,7 +139,7 @@ def test_model_names_every_tensor_of_its_checkpoint():
 
 
 def test_the_measurement_configurations_are_valid():
-    """What `bench.py --design bonolorn` builds at its sizes parses as Bonolorn, Riruzen, Qwen3 and Nelovik configurations."""
+    """What `bench.py --design ...` builds at its sizes parses as Bonolorn, Riruzen, Qwen3, Nelovik and Venitar configurations."""
     import sys
 
     from conftest import ROOT
@@ -148,7 +148,7 @@ def test_the_measurement_configurations_are_valid():
     from lucciola_b200.config import resolve_architecture
     for size in bench.DESIGN_SIZES.values():
         cfgs = bench.design_configs(size, 4, 4096)
-        assert set(cfgs) == {"bonolorn", "riruzen", "qwen3", "nelovik"}
+        assert set(cfgs) == {"bonolorn", "riruzen", "qwen3", "nelovik", "venitar"}
         for name, cfg in cfgs.items():
             arch = resolve_architecture(cfg)
             arch.config_from_dict(cfg)
