@@ -488,7 +488,7 @@ def design_configs(size: dict, layers: int, positions: int) -> dict:
         "left": {"heads": H // 2, "kv_heads": max(H // 8, 1), "dim": D, "vdim": D, "scale": D ** -0.5,
                  "rot": {"dims": D // 2, "base": 1e6, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}, "mask": {"size": 1024}},
         "right": {"heads": H // 2, "kv_heads": max(H // 4, 1), "dim": D, "vdim": D, "conv": 4, "decay_rank": 64, "gate_rank": 64},
-        "left_scale": 0.8, "right_scale": 0.9}}
+        "left_scale": 0.6, "right_scale": 1.1}}
     def ret(ff):
         return {"type": "retention", "mlp": ff, "mixer": {"heads": H, "dim": D, "vdim": D, "rot": {"dims": D, "base": 1e6},
                                                           "decay": [1.0 - 2.0 ** -(3 + 8 * h / max(H - 1, 1)) for h in range(H)]}}
@@ -496,7 +496,7 @@ def design_configs(size: dict, layers: int, positions: int) -> dict:
                                                        "rot": {"dims": D // 2, "base": 1e4}, "mask": {"size": 1024}}}
     vorder = [vpair, ret(None), vatt, ret(ffd)]
     looped = layers >= 4
-    venitar = {"architecture": "Venitar", "vocab": size["vocab"], "width": W, "embedding": {"scale": 0.5}, "norm": {"eps": 1e-6},
+    venitar = {"architecture": "Venitar", "vocab": size["vocab"], "width": W, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
                "loop": {"start": 0, "stop": 2 if looped else 0, "times": 2 if looped else 1},
                "layers": [vorder[i % 4] for i in range(layers - 2 if looped else layers)]}
     return {"riruzen": riruzen, "qwen3": qwen3, "bonolorn": bonolorn, "nelovik": nelovik, "venitar": venitar}

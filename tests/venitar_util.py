@@ -53,7 +53,7 @@ def _config(vocab, width, eps, scale, loop, layers):
 # B: everything that can be 1 is 1: one head each, one tap (no convolution state), a window and a chunk of one token, rank
 #    1, one pass of the loop, an embedding scale of 1, no rotation in one mixer and the whole head in another.
 # C: sizes at which the bfloat16 engine takes its tensor-core kernels (multiples of 64), windows and chunks across
-#    several pages, as many kv heads as heads, three passes over the first two layers, state rows of 128.
+#    several pages, as many kv heads as heads, three passes over the two middle layers, state rows of 128.
 # D: heads of 128, a window and a chunk longer than any test sequence, state rows of 200 and 256, value columns that
 #    fill no tile, the loop over all layers.
 CONFIGS = {
@@ -66,14 +66,14 @@ CONFIGS = {
         _pair(_left(1, 1, 16, 16, 0.25, _rot(16, 100.0, (1.0, 8, 4.0, 2.0)), 1), _right(1, 1, 40, 40, 1, 1, 1), 1.0, 1.0, 32),
         _retention(1, 16, 24, (0.95,), _rot(0, 100.0), 64),
         _attention(1, 1, 16, 0.3, _rot(16, 100.0), 1, None)]),
-    "C": _config(331, 256, 1e-5, 0.5, (0, 2, 3), [
-        _attention(4, 4, 64, 0.125, _rot(32, 1000000.0), 40, 512),
-        _pair(_left(8, 2, 64, 64, 0.125, _rot(64, 10000.0, (2.0, 128, 16.0, 2.0)), 33), _right(4, 2, 128, 64, 4, 16, 8), 0.8, 0.9, 256),
+    "C": _config(331, 256, 1e-5, 0.25, (1, 3, 3), [
+        _attention(4, 4, 64, 0.125, _rot(32, 500000.0), 40, 512),
+        _pair(_left(8, 2, 64, 64, 0.125, _rot(64, 10000.0, (3.0, 128, 16.0, 2.0)), 33), _right(4, 2, 128, 64, 4, 16, 8), 0.75, 1.25, 256),
         _retention(4, 64, 64, (0.9, 0.97, 0.995, 0.9995), _rot(64, 10000.0), 256),
         _attention(8, 2, 64, 0.125, _rot(64, 10000.0), 64, None)]),
     "D": _config(150, 256, 1e-6, 2.0, (0, 3, 2), [
         _pair(_left(4, 2, 128, 96, 0.09, _rot(64, 10000.0), 1000), _right(2, 1, 200, 48, 4, 8, 24), 1.2, 0.7, 128),
-        _retention(2, 256, 40, (0.98, 0.9999), _rot(128, 250000.0), None),
+        _retention(2, 256, 40, (0.98, 0.9999), _rot(128, 300000.0), None),
         _attention(2, 1, 128, 0.09, _rot(128, 10000.0), 1000, 128)]),
 }
 PAGE = {"A": 16, "B": 8, "C": 16, "D": 16}
